@@ -1,35 +1,42 @@
 // Prefill: grouped NVFP4 GEMMs on the 5th-generation tensor cores (tcgen05, accumulators in TMEM).
 //
-// Tiles: D[128 weight rows per CTA x N tokens] += A[128 x 64] * B[N x 64]^T per pipeline stage, N <= 256
-// (multiples of 32: a small expert runs a small N), kind::f16, fp32 accumulate.  By default two CTAs of a cluster
-// work as a pair (cta_group::2): one MMA spans 256 weight rows over both SMs, each CTA unpacks its own 128 rows
-// and fetches half of the token rows.  A is the expert's packed E2M1 rows, unpacked and multiplied by the E4M3
-// block scale in registers (both steps exact in bf16) and stored into the 128-byte-swizzled K-major layout the
-// MMA descriptors describe; B (bf16 activation rows, gathered through the token permutation for gate_up,
-// contiguous for down) arrives asynchronously: for gate_up by 16-byte async copies whose completion an mbarrier
-// counts (nobody waits for them in program order), for down by TMA boxes of 64 rows.  The per-row fp32 global
-// scale, the SwiGLU and the router weight are applied to the fp32 accumulator in the epilogue with the
-// reference's bf16 rounding points.
+// One work item = (token tile of one expert, 256 weight rows), computed by a PAIR of CTAs (cluster of two,
+// tcgen05 cta_group::2) as D[tokens x 256 weight rows] += A[tokens x 64] * B[256 x 64]^T per k-step, kind::f16
+// with fp16 operands, fp32 accumulation.
+//   A = token rows, fp16.  They are contiguous: a pre-pass gathers x through the permutation into expert order,
+//       scaled per row by a power of two into fp16 range (exact; the epilogue multiplies the inverse back); the
+//       down GEMM reads the ic2 rows the gate_up GEMM wrote, already in expert order.  One thread per CTA asks the
+//       TMA unit for boxes of 64 rows x 64 k (128-byte swizzle).  Each CTA of the pair holds its own token rows:
+//       128 of a 256-token tile, or 64 of a tile with at most 128 tokens (M = 128 over the pair costs half the
+//       tensor time of M = 256).
+//   B = weight rows.  Each CTA unpacks 128 of the item's 256 rows: E2M1 codes -> f16x2 (cvt), times the E4M3 block
+//       scale converted to f16x2 (one multiply, exact: at most 6 significant bits, range 2^-10 .. 2688), stored
+//       into the 128-byte-swizzled K-major layout the MMA descriptor describes.  The packed bytes and scales
+//       come through a staging ring in shared memory that a second TMA thread fills four k-steps at a time
+//       (128 contiguous bytes of every row), so the unpack warps never have a global load in flight: a warp
+//       whose threads each read their own row from global memory touches 32 cache lines per instruction, and
+//       the SM's load/store pipe (one line per cycle, shared with every shared-memory store) was the bottleneck
+//       of that form; a proxy fence or barrier arrive also waits for the thread's loads.
+//   D   TMEM lane = token, column = weight row: an epilogue thread owns ONE token and reads consecutive output
+//       columns, so SwiGLU pairs sit in one thread (gate and up rows interleave inside an item).  Four lanes
+//       exchange their pieces before they store, so that one store instruction writes whole 128-byte lines.
+//       The fp32 per-row global, the SwiGLU and the router weight are applied here with the reference's bf16
+//       rounding points.
+// The MMA time of an instruction is proportional to N and independent of M (measured: 128 cycles for N = 256,
+// 64 for N = 128, for M = 128 as for M = 64 rows per CTA), so weights fill N and the tokens stream through M.
 //
-// Roles in a CTA (one persistent CTA per SM, static round-robin over the tile list); in a pair gate_up runs 832
-// threads (4 + 16 + 4 + 1 + 1 warps), down 864 (8 + 16 + 1 + 1 + 1); a lone CTA has no relay warp:
-//   epilogue warps    TMEM -> registers -> global (warp w owns TMEM lanes 32 (w%4) .. +31 = weight rows and, with
-//                     eight warps, every other 16-column chunk; the next chunk's TMEM load is in flight while one
-//                     is finished)
-//   16 unpack warps   in two groups of eight; group g fills the A half of the ring stages of the k-steps with
-//                     parity g, so one group's unpack overlaps the other's and two MMA steps cover it; a thread
-//                     owns half a row of a stage (32 codes + 2 scales) and requests its bytes four of its own
-//                     steps ahead
-//   token warps       gate_up: four warps wait for a free stage, issue its 16-byte copies and hand their completion
-//                     to the barrier; down: one thread posts the byte count and issues the TMA box copies
-//   relay warp        pair only: lane 0 forwards "this CTA's part of the stage is complete" to the leader's barrier
-//   MMA warp          lane 0 (of the pair's leader) issues tcgen05.mma / tcgen05.commit; the warp owns the TMEM
-//                     allocation
-// (The TMA unit's tile::gather4 copy was measured for the token rows and dropped: about 56 cycles per four-row
-// copy, 3.6k cycles for a 256-row stage against 0.5k cycles of MMA.)
+// Warp roles (one persistent CTA pair per two SMs, static round-robin over the item list):
+//   epilogue warps   TMEM -> registers -> global; warp w may touch TMEM lanes 32 (w % 4) .. +31
+//   16 unpack warps  four groups of four; group g fills the B slot of the k-steps with index = g mod 4, one thread
+//                    per weight row (64 k = 32 packed bytes + 4 scales), so four k-steps are in production at once
+//   token TMA warp   lane 0 posts the byte count (leader) and issues this CTA's token boxes
+//   weight TMA warp  lane 0 fills the packed-weight staging ring of this CTA
+//   relay warp       lane 0 forwards "this CTA's weight half of the k-step is stored" to the leader's barrier
+//   MMA warp         lane 0 of the pair's leader issues tcgen05.mma / tcgen05.commit; the warp owns the TMEM
 // Every mbarrier wait is bounded: on time-out the CTA records a status word, stops, frees its TMEM.
 #include <algorithm>
 #include <cstdlib>
+#include <mutex>
 
 #include <cuda.h>  // CUtensorMap (types only; the encoder is looked up at run time)
 
@@ -37,43 +44,59 @@
 
 namespace b200moe {
 
-constexpr int BK = 64, MAX_STAGES = 6;
-constexpr int DQ_WARPS = 16, DQ_GROUPS = 2, DQ_GROUP_WARPS = DQ_WARPS / DQ_GROUPS;
-// Warp roles by mode (0 = gate_up + SwiGLU, 1 = down): epilogue warps first, then the unpackers, the token warps,
-// the MMA warp.  gate_up moves its token rows with async copies from four warps and gets by with four epilogue
-// warps; down has four times as many outputs per MMA step and one TMA thread for its token rows.
-// PAIR: two CTAs of a cluster share one 256-row x N tile (tcgen05 cta_group::2): each unpacks its own 128 weight
-// rows and fetches only half of the token rows, the tensor cores of both SMs read both halves.  A pair's gate_up
-// CTA has one more warp whose lane 0 forwards "this CTA's part of the stage is complete" to the leader's barrier
-// (the producers themselves only arrive locally: a cluster-scope arrive from a thread with global loads in flight
-// waits for them).
-template <int MODE, bool PAIR>
+constexpr int BK = 64;
+constexpr int TOK_ROWS = 128;                        // token rows a CTA holds per k-step (64 used in the half form)
+constexpr int WROWS = 128;                           // weight rows a CTA unpacks per k-step
+constexpr int ITEM_N = 2 * WROWS;                    // weight rows per item (the MMA's N)
+constexpr int TN = 2 * TOK_ROWS;                     // tokens per full tile
+constexpr int A_BYTES = TOK_ROWS * BK * 2, B_BYTES = WROWS * BK * 2;
+constexpr int UNPACK_WARPS = 16, GROUPS = 4, GROUP_WARPS = UNPACK_WARPS / GROUPS;
+constexpr int SUPER = GROUPS;                        // k-steps per staged weight block: 128 packed bytes of every row
+constexpr int W_PACKED_BYTES = WROWS * (SUPER * BK / 2), W_SCALE_BYTES = WROWS * (SUPER * BK / 16);
+constexpr int W_BYTES = W_PACKED_BYTES + W_SCALE_BYTES;
+// Ring depths.  Tokens: six k-steps; unpacked weights: four (one per unpack group); staged packed weights: three
+// blocks of four k-steps.
+constexpr int SA = 6, SB = 4, SW = 3;
+constexpr int TMEM_COLS = 512;
+static_assert(GROUP_WARPS * 32 == WROWS, "one unpack thread per weight row of a k-step");
+static_assert(W_PACKED_BYTES % 1024 == 0 && W_BYTES % 1024 == 0, "swizzled tiles start on 1024-byte boundaries");
+
+// Warp roles by mode (0 = gate_up + SwiGLU, 1 = down x router weight).  The down GEMM has a quarter of the k-steps
+// per item and twice the output bytes, so it gets eight epilogue warps.
+template <int MODE>
 struct Roles {
   static constexpr int EPI = MODE == 0 ? 4 : 8;
-  static constexpr int TOK = MODE == 0 ? 4 : 1;
-  static constexpr int RELAY = PAIR ? 1 : 0;
-  static constexpr int TOK0 = EPI + DQ_WARPS, RELAY0 = TOK0 + TOK, MMA = RELAY0 + RELAY, THREADS = (MMA + 1) * 32;
-  static constexpr int BROWS = PAIR ? 128 : 256;           // token rows a CTA holds per stage
-  static constexpr int STAGE_BYTES = 128 * BK * 2 + BROWS * BK * 2;
-  static constexpr int STAGES = PAIR ? 6 : 4;
+  static constexpr int UNPACK0 = EPI, TMA_A = EPI + UNPACK_WARPS, TMA_W = TMA_A + 1, RELAY = TMA_W + 1, MMA = RELAY + 1;
+  static constexpr int THREADS = (MMA + 1) * 32;
+  // Registers per thread after the roles have traded them (setmaxnreg; roles are whole warpgroups of four warps):
+  // the kernel starts with 65536 / THREADS rounded down to a multiple of 8, the unpack and the single-thread roles
+  // give registers back, the epilogue warps take them.
+  static constexpr int REGS_EPI = MODE == 0 ? 168 : 104, REGS_UNPACK = MODE == 0 ? 72 : 64, REGS_MISC = MODE == 0 ? 56 : 48;
+  static_assert(EPI % 4 == 0 && UNPACK_WARPS % 4 == 0 && MMA + 1 - TMA_A == 4, "roles are whole warpgroups");
+  static_assert(EPI * 32 * REGS_EPI + UNPACK_WARPS * 32 * REGS_UNPACK + 128 * REGS_MISC <= 65536, "register file");
 };
-constexpr int TMEM_COLS = 512;
+template <int N>
+B200MOE_DEVICE void regs_take() {  }
+template <int N>
+B200MOE_DEVICE void regs_give() {  }
 
 struct GgParams {
-  CUtensorMap a_map;             // mode 1: ic2 [sorted position, K] as 64-column x 64-row boxes, 128B swizzle
-  const __nv_bfloat16* a;        // mode 0: x [T, lda]; mode 1: ic2 [sorted position, lda]
-  int64_t lda;
+  CUtensorMap a_map;             // token rows [positions, K] fp16 as 64-column x 64-row boxes, 128B swizzle
+  CUtensorMap w_map;             // packed weights [slots, N, K/2] bytes as 128-byte x 64-row boxes, 128B swizzle
+  CUtensorMap s_map;             // block scales [slots, N, K/16] bytes as 16-byte x 64-row boxes
   const uint8_t* packed;         // [slots, N, K/2]
   const uint8_t* scales;         // [slots, N, K/16]
   const float* globals;          // [slots, N]
   int64_t packed_stride, scale_stride, global_stride;  // bytes from one slot to the next
-  int N, K, NT;                  // weight rows, reduction length, column tiles per row tile
-  const int4* mtiles;            // {slot, first sorted position, rows, 0}
+  int N, K, NT;                  // weight rows, reduction length, items per token tile
+  int half_n;                    // mode 0: intermediate size (gate rows [0, half_n), up rows [half_n, N))
+  int w_staged;                  // 1: packed weights come through the staging ring (K a multiple of 256)
+  const int4* mtiles;            // {slot, first sorted position, rows, 1 if the tile runs in the half form}
   const int32_t* num_mtiles;
   const int32_t* sorted_routes;  // sorted position -> flat route id
   const float* topk_w;           // [routes]
-  int top_k, mode;
-  __nv_bfloat16* out;            // mode 0: ic2 [pos, I]; mode 1: ic3 [route, H]
+  const float* a_inv;            // mode 0: inverse of the power-of-two scale of every token row
+  void* out;                     // mode 0: ic2 [pos, half_n] fp16; mode 1: ic3 [route, N] bf16
   __nv_bfloat16* const* out_peers;  // mode 1, expert parallel: ic3 of every rank (peer-mapped), or null
   int routes_per_rank;           // global route g belongs to rank g / routes_per_rank
   int64_t route_offset;          // global route = (local route + route_offset) mod total_routes: a call covers a slice of
@@ -90,18 +113,6 @@ B200MOE_DEVICE void mbar_arrive(uint32_t bar) {
 }
 B200MOE_DEVICE void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-// One box of the 2-D tensor behind `map`, starting at (col, row), -> shared memory at `dst` (swizzled by
-// address); completion is counted in bytes on `bar`.
-B200MOE_DEVICE void tma_load_2d(uint32_t dst, const CUtensorMap* map, int col, int row, uint32_t bar) {
-  asm volatile("cp.async.bulk.tensor.2d.shared::cta.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-               ::"r"(dst), "l"(map), "r"(col), "r"(row), "r"(bar)
-               : "memory");
-}
-// The calling thread's earlier cp.async copies arrive on `bar` when they have landed (the arrival is one of the
-// barrier's expected count).
-B200MOE_DEVICE void cp_async_arrive_noinc(uint32_t bar) {
-  asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
 }
 B200MOE_DEVICE uint32_t cluster_ctarank() {
   uint32_t r;
@@ -121,7 +132,7 @@ B200MOE_DEVICE void cluster_sync_all() {
   asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
 // cta_group::2 forms: the MMA spans both CTAs of the pair, the commit arrives on the same barrier offset in every
-// CTA of `mask`, the TMA copy lands in this CTA and counts its bytes on the leader's barrier.
+// CTA of `mask` (an arrive, not a load), the TMA box lands in this CTA and counts its bytes on the leader's barrier.
 B200MOE_DEVICE void tc_commit_pair(uint32_t bar, uint16_t mask) {
   asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
                ::"r"(bar), "h"(mask) : "memory");
@@ -129,6 +140,12 @@ B200MOE_DEVICE void tc_commit_pair(uint32_t bar, uint16_t mask) {
 B200MOE_DEVICE void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, int col, int row, uint32_t leader_bar) {
   asm volatile("cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
                ::"r"(dst), "l"(map), "r"(col), "r"(row), "r"(leader_bar)
+               : "memory");
+}
+// One box of a 3-D tensor -> this CTA's shared memory; completion is counted in bytes on this CTA's barrier.
+B200MOE_DEVICE void tma_load_3d(uint32_t dst, const CUtensorMap* map, int c0, int c1, int c2, uint32_t bar) {
+  asm volatile("cp.async.bulk.tensor.3d.shared::cta.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+               ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(bar)
                : "memory");
 }
 B200MOE_DEVICE bool mbar_try_wait(uint32_t bar, uint32_t parity) {
@@ -140,27 +157,15 @@ B200MOE_DEVICE bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 // Bounded wait.  false = gave up (time limit, or another thread of the CTA already did).  The clock is the SM's
-// cycle counter (cheap to read); the limit is about two seconds at 2 GHz.  A waiter that is not served at once
-// sleeps `sleep_ns` between polls: two dozen warps share four schedulers, and a warp that spins on a barrier takes
-// issue slots from the warps it is waiting for.
-B200MOE_DEVICE bool mbar_test_wait(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile("{\n\t.reg .pred p;\n\tmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
-               : "=r"(ok)
-               : "r"(bar), "r"(parity)
-               : "memory");
-  return ok != 0;
-}
-template <int SLEEP_NS = 64>
+// cycle counter; the limit is about two seconds at 2 GHz.  mbarrier.try_wait suspends the thread until the phase
+// completes or a short hardware time limit passes, so the loop itself issues few instructions.
 B200MOE_DEVICE bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
-  if (SLEEP_NS == 0 && mbar_test_wait(bar, parity)) return true;  // critical-path waiter: a plain test first
-  for (int i = 0; i < 4; ++i)
+  for (int i = 0; i < 8; ++i)
     if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
   for (uint32_t i = 1;; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
-    if (SLEEP_NS > 0) __nanosleep(SLEEP_NS);
-    if ((i & 255u) == 0u) {
+    if ((i & 63u) == 0u) {
       if (*abort_flag) return false;
       if (clock64() - t0 > 4000000000ll) {
         *abort_flag = 1;
@@ -171,15 +176,6 @@ B200MOE_DEVICE bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort
 }
 B200MOE_DEVICE void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 B200MOE_DEVICE void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-B200MOE_DEVICE void tc_commit(uint32_t bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-B200MOE_DEVICE void tc_mma_f16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
-  asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-               "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-               ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
-               : "memory");
-}
 B200MOE_DEVICE void tc_mma_f16_pair(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
   asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
                "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
@@ -201,7 +197,7 @@ B200MOE_DEVICE void tc_ld16(uint32_t taddr, uint32_t (&r)[16]) {
       : "r"(taddr));
 }
 // 16 bytes that nobody on this SM reads again (no L1 allocation); a miss in L2 brings in the whole 128-byte line,
-// because the next three k-steps of the same weight row read its other sectors.
+// because the next k-steps of the same weight row read its other sectors.
 B200MOE_DEVICE uint4 ldg_nc_v4_l2line(const void* p) {
   uint4 r;
   asm volatile("ld.global.nc.L1::no_allocate.L2::128B.v4.u32 {%0,%1,%2,%3}, [%4];"
@@ -209,591 +205,570 @@ B200MOE_DEVICE uint4 ldg_nc_v4_l2line(const void* p) {
                : "l"(p));
   return r;
 }
-B200MOE_DEVICE uint32_t ldg_nc_u16(const void* p) {
-  unsigned short r;
-  asm volatile("ld.global.nc.u16 %0, [%1];" : "=h"(r) : "l"(p));
+B200MOE_DEVICE uint4 lds_v4(uint32_t addr) {
+  uint4 r;
+  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w) : "r"(addr));
   return r;
 }
-// f16x2 holding E2M1 values (never subnormal, zero allowed) -> the bf16x2 bit pattern of value * 2^-112: the
-// five exponent bits land in the low end of bf16's eight, the mantissa's leading bits stay, zero stays zero.
-// Multiplying by bf16(block scale * 2^112) then gives value * scale exactly (at most five significant bits).
-B200MOE_DEVICE uint32_t e2m1_f16x2_times_scale(uint32_t h, uint32_t scale_bf16x2) {
-  const uint32_t t = ((h >> 3) & 0x0fff0fffu) | (h & 0x80008000u);
+B200MOE_DEVICE uint32_t lds_u32(uint32_t addr) {
   uint32_t r;
-  asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(t), "r"(scale_bf16x2));
+  asm volatile("ld.shared.u32 %0, [%1];" : "=r"(r) : "r"(addr));
   return r;
 }
-// Four bytes of packed E2M1 (8 codes) x one block scale -> one 16-byte chunk of bf16
-B200MOE_DEVICE uint4 unpack_chunk(uint32_t w, uint32_t scale_bf16x2) {
+// Four bytes of packed E2M1 (8 codes) x one block scale (f16x2, both halves equal) -> 16 bytes of fp16, exact
+B200MOE_DEVICE uint4 unpack_chunk_f16(uint32_t w, uint32_t scale2) {
   uint32_t h[4];
   e2m1x8_to_f16x2(w, h);
-  return make_uint4(e2m1_f16x2_times_scale(h[0], scale_bf16x2), e2m1_f16x2_times_scale(h[1], scale_bf16x2),
-                    e2m1_f16x2_times_scale(h[2], scale_bf16x2), e2m1_f16x2_times_scale(h[3], scale_bf16x2));
+  return make_uint4(hmul2_u32(h[0], scale2), hmul2_u32(h[1], scale2), hmul2_u32(h[2], scale2), hmul2_u32(h[3], scale2));
 }
 B200MOE_DEVICE void sts_v4(uint32_t addr, const uint4& v) {
   asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
 }
+B200MOE_DEVICE void stg_v4(void* p, const uint4& v) {
+  asm volatile("st.global.v4.b32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+// two floats -> f16x2, values beyond the fp16 range saturate to +-65504
+B200MOE_DEVICE uint32_t pack_f16x2_sat(float lo, float hi) {
+  uint32_t r;
+  asm("cvt.rn.satfinite.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+  return r;
+}
+// 4 x 4 transpose of register blocks inside a quad of lanes (lane & 3 = j): on entry lane j holds its own blocks
+// b[0..3]; on return b[k] is block j of lane k of the quad.  Two exchange rounds (lane ^ 1, lane ^ 2).
+template <int NR>
+B200MOE_DEVICE void quad_transpose(uint32_t (&b)[4][NR], int j) {
+  const bool odd = j & 1, hi = j & 2;
+#pragma unroll
+  for (int m = 0; m < 2; ++m)
+#pragma unroll
+    for (int r = 0; r < NR; ++r) {
+      const uint32_t send = odd ? b[2 * m][r] : b[2 * m + 1][r];
+      const uint32_t got = __shfl_xor_sync(0xffffffffu, send, 1);
+      if (odd) b[2 * m][r] = got;
+      else b[2 * m + 1][r] = got;
+    }
+#pragma unroll
+  for (int s = 0; s < 2; ++s)
+#pragma unroll
+    for (int r = 0; r < NR; ++r) {
+      const uint32_t send = hi ? b[s][r] : b[s + 2][r];
+      const uint32_t got = __shfl_xor_sync(0xffffffffu, send, 2);
+      if (hi) b[s][r] = got;
+      else b[s + 2][r] = got;
+    }
+}
 
-// For gate_up the tile's rows interleave gate and up (row 2i = gate n0+i, row 2i+1 = up n0+i): the two values a
-// SwiGLU needs sit in neighbouring lanes and are exchanged with one shuffle.
-constexpr int WM = 128, TN = 256;
-constexpr int WA_STAGE = WM * BK * 2;
-
-struct alignas(16) WsShared {
-  unsigned long long full[MAX_STAGES], empty[MAX_STAGES], part[MAX_STAGES], tmem_full[2], tmem_empty[2], table[2];
+struct alignas(16) GgShared {
+  unsigned long long full_a[SA], empty_a[SA], full_b[SB], empty_b[SB], part[SB], full_w[SW], empty_w[SW];
+  unsigned long long tmem_full[2], tmem_empty[2], table[2];
   uint32_t tmem_base;
   int abort_flag;
-  unsigned long long dst[2][TN];  // mode 1: destination row of every token column (element address), per accumulator buffer
-  alignas(16) float wgt[2][TN];   // mode 1: router weight of every token column
+  alignas(16) float gl[2][ITEM_N];  // per accumulator buffer: the fp32 global of every column of the item
 };
-constexpr size_t WS_SMEM = 1024 + (size_t)4 * (WA_STAGE + TN * BK * 2) + sizeof(WsShared);
-static_assert(6 * (WA_STAGE + (TN / 2) * BK * 2) == 4 * (WA_STAGE + TN * BK * 2), "both ring shapes use the same bytes");
+constexpr size_t GG_SMEM = 1024 + (size_t)SA * A_BYTES + (size_t)SB * B_BYTES + (size_t)SW * W_BYTES + sizeof(GgShared);
 
-// kind::f16 instruction descriptor: D fp32, A and B bf16 (the two 16-bit formats cannot be mixed: a bf16 x fp16
-// descriptor raises an illegal-instruction fault), both K-major, M = 128, N = n.
-B200MOE_DEVICE uint32_t umma_idesc_n(int n, int m) {
-  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
-}
-B200MOE_DEVICE uint2 ldg_nc_v2_na(const void* p) {
-  uint2 r;
-  asm volatile("ld.global.nc.L1::no_allocate.v2.u32 {%0,%1}, [%2];" : "=r"(r.x), "=r"(r.y) : "l"(p));
-  return r;
-}
-B200MOE_DEVICE uint32_t ldg_nc_u8(const void* p) {
-  uint32_t r;
-  asm volatile("ld.global.nc.u8 %0, [%1];" : "=r"(r) : "l"(p));
-  return r;
+// kind::f16 instruction descriptor: D fp32, A and B fp16, both K-major, M = m (over the pair), N = n.
+B200MOE_DEVICE uint32_t umma_idesc_f16(int n, int m) {
+  return (1u << 4) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
 }
 
-#ifdef B200MOE_GG_PROFILE
-__device__ long long g_gg_prof[2][160][16];
-#define PROF_T0 const long long _t0 = clock64();
-#define PROF_ADD(var) var += clock64() - _t0;
-#else
-#define PROF_T0
-#define PROF_ADD(var)
-#endif
-
-template <int MODE, bool PAIR>
-__global__ void __launch_bounds__(Roles<MODE, PAIR>::THREADS, 1) grouped_gemm_ws_kernel(const __grid_constant__ GgParams p) {
-  using R = Roles<MODE, PAIR>;
-  constexpr int EPI_WARPS = R::EPI, TOK_WARPS = R::TOK, TOK_WARP0 = R::TOK0, RELAY_WARP = R::RELAY0, MMA_WARP = R::MMA;
-  constexpr int STAGES = R::STAGES, WSTAGE_BYTES = R::STAGE_BYTES, BROWS = R::BROWS;
+template <int MODE>
+__global__ void __launch_bounds__(Roles<MODE>::THREADS, 1) grouped_gemm_kernel(const __grid_constant__ GgParams p) {
+  using R = Roles<MODE>;
+  constexpr int EPI_WARPS = R::EPI;
   extern __shared__ unsigned char smem_dyn[];
   unsigned char* ring = reinterpret_cast<unsigned char*>(((uintptr_t)smem_dyn + 1023) & ~(uintptr_t)1023);
-  WsShared* sh = reinterpret_cast<WsShared*>(ring + (size_t)STAGES * WSTAGE_BYTES);
+  GgShared* sh = reinterpret_cast<GgShared*>(ring + (size_t)SA * A_BYTES + (size_t)SB * B_BYTES + (size_t)SW * W_BYTES);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const uint32_t ring_u32 = smem_u32(ring);
+  const uint32_t ring_a = smem_u32(ring), ring_b = ring_a + SA * A_BYTES, ring_w = ring_b + SB * B_BYTES;
   volatile int* abort_flag = &sh->abort_flag;
-  // a pair walks the tile list together: CTA `rank` owns weight tile 2*wp + rank of pair-tile (tt, wp) and the
-  // token rows rank * npad/2 .. of the token tile; a lone CTA is "pair" blockIdx.x of gridDim.x with rank 0
-  const int rank = PAIR ? (int)cluster_ctarank() : 0;
-  const int unit = PAIR ? (int)(blockIdx.x >> 1) : (int)blockIdx.x, units = PAIR ? (int)(gridDim.x >> 1) : (int)gridDim.x;
-  const int WPT = PAIR ? p.NT >> 1 : p.NT;  // work items per token tile
+  const int rank = (int)cluster_ctarank();
+  const int unit = (int)(blockIdx.x >> 1), units = (int)(gridDim.x >> 1);
 
   if (tid == 0) {
-    for (int s = 0; s < STAGES; ++s) {
-      // arrivals that complete this CTA's part of a stage: the unpack group's warps, plus every token thread
-      // (mode 0) or the thread that posts the TMA byte count (mode 1).  A lone CTA counts them on `full`; in a pair
-      // each CTA counts its own on `part`, and `full` (the leader's) gets one arrival per relay plus the byte count.
-      constexpr int LOCAL = DQ_GROUP_WARPS + (MODE == 0 ? TOK_WARPS * 32 : 0);
-      mbar_init(smem_u32(&sh->full[s]), PAIR ? 2 + (MODE == 1 ? 1 : 0) : LOCAL + (MODE == 1 ? 1 : 0));
-      mbar_init(smem_u32(&sh->empty[s]), 1);
-      mbar_init(smem_u32(&sh->part[s]), LOCAL);
+    for (int s = 0; s < SA; ++s) {
+      mbar_init(smem_u32(&sh->full_a[s]), 1);            // the leader's byte-count arrive (+ the bytes of both CTAs)
+      mbar_init(smem_u32(&sh->empty_a[s]), 1);           // the MMA thread's commit
+    }
+    for (int s = 0; s < SB; ++s) {
+      mbar_init(smem_u32(&sh->full_b[s]), 2);            // one relay per CTA
+      mbar_init(smem_u32(&sh->empty_b[s]), 1);           // the MMA thread's commit
+      mbar_init(smem_u32(&sh->part[s]), GROUP_WARPS);    // this CTA's unpack warps of the k-step's group
+    }
+    for (int s = 0; s < SW; ++s) {
+      mbar_init(smem_u32(&sh->full_w[s]), 1);            // the weight TMA thread's byte-count arrive (+ bytes)
+      mbar_init(smem_u32(&sh->empty_w[s]), UNPACK_WARPS);  // every unpack warp has read its part of the block
     }
     for (int b = 0; b < 2; ++b) {
-      mbar_init(smem_u32(&sh->tmem_full[b]), 1);
-      mbar_init(smem_u32(&sh->tmem_empty[b]), (PAIR ? 2 : 1) * EPI_WARPS);
       mbar_init(smem_u32(&sh->table[b]), EPI_WARPS * 32);
+      mbar_init(smem_u32(&sh->tmem_full[b]), 1);
+      mbar_init(smem_u32(&sh->tmem_empty[b]), 2 * EPI_WARPS);
     }
     sh->abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  if (warp == MMA_WARP) {
-    if (PAIR) {
-      asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sh->tmem_base)),
-                   "r"((uint32_t)TMEM_COLS)
-                   : "memory");
-      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
-    } else {
-      asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sh->tmem_base)),
-                   "r"((uint32_t)TMEM_COLS)
-                   : "memory");
-      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-    }
+  if (warp == R::MMA) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sh->tmem_base)),
+                 "r"((uint32_t)TMEM_COLS)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
   }
   tc_fence_before();
   __syncthreads();
-  if (PAIR) cluster_sync_all();  // the other CTA's barriers exist before anyone arrives on them
+  cluster_sync_all();  // the other CTA's barriers exist before anyone arrives on them
   tc_fence_after();
   const uint32_t tmem_base = sh->tmem_base;
-  const int total_tiles = (*p.num_mtiles) * WPT;   // mtiles: token tiles {slot, first sorted position, rows<=256, padded rows}
+  const int NT = p.NT;
+  const int total_items = (*p.num_mtiles) * NT;
   const int KB = p.K / BK;
-  const int half_n = p.N >> 1;
-  // barriers of the pair's leader (rank 0), as seen from this CTA
-  auto leader = [&](const unsigned long long* bar) { return PAIR ? mapa_rank(smem_u32(bar), 0) : smem_u32(bar); };
+  const int my_items = total_items > unit ? (total_items - unit + units - 1) / units : 0;
+  const uint32_t total_steps = (uint32_t)my_items * (uint32_t)KB;  // k-steps of this pair over all its items
+  auto leader = [&](const unsigned long long* bar) { return mapa_rank(smem_u32(bar), 0); };
+  // weight row (of the slot's matrix) behind row j of item column order: gate_up items interleave gate and up
+  auto weight_row = [&](int wt, int j) {
+    if (MODE == 0) return (j & 1) ? p.half_n + wt * (ITEM_N / 2) + (j >> 1) : wt * (ITEM_N / 2) + (j >> 1);
+    return wt * ITEM_N + j;
+  };
 
   if (warp < EPI_WARPS) {
     // ------------------------------------------------------------------ epilogue
-    // warp w: TMEM lanes 32 (w % 4) .. +31 (the lanes a warp may touch), 16-column chunks with parity w / 4
-    const int row = (warp & 3) * 32 + lane;  // weight-tile row == TMEM lane
-    const int csel = warp >> 2;
-    const bool odd = lane & 1;
+    regs_take<R::REGS_EPI>();
+    // warp w: TMEM lanes 32 (w % 4) .. +31 (the lanes a warp may touch); with eight warps, w / 4 picks the column half
+    const int q = warp & 3, hsel = warp >> 2, jq = lane & 3;
+    constexpr int CH = EPI_WARPS / 4;
+    constexpr int NR = MODE == 0 ? 4 : 8;   // registers of one 16-column chunk after conversion (8 fp16 / 16 bf16)
     int tl = 0;
-    long long pw = 0, ptot = clock64(), ptab = 0, pchunk = 0;
-    for (int tile = unit; tile < total_tiles; tile += units, ++tl) {
-#ifdef B200MOE_GG_PROFILE
-      const long long _tt0 = clock64();
-#endif
-      const int tt = tile / WPT, wt = PAIR ? 2 * (tile - tt * WPT) + rank : tile - tt * WPT;
+    for (int item = unit; item < total_items; item += units, ++tl) {
+      const int tt = item / NT, wt = item - tt * NT;
       const int4 info = p.mtiles[tt];
-      const int buf = tl & 1;
-      const int rows = info.z, npad = info.w;
-      int wrow;  // weight row of this thread
-      if (MODE == 0) wrow = (row & 1) ? half_n + wt * 64 + (row >> 1) : wt * 64 + (row >> 1);
-      else wrow = wt * WM + row;
-      const float g_mine = p.globals[(int64_t)info.x * (p.global_stride >> 2) + wrow];
-      if (MODE == 1) {
-        // destination row and router weight of every token column: one entry per epilogue thread.  The table is
-        // double-buffered like the accumulator: a warp that runs ahead fills the other buffer and then waits here.
-        if (tid < npad) {
-          const int pos = info.y + min(tid, rows - 1);
-          const int route = p.sorted_routes[pos];
-          __nv_bfloat16* base = p.out + (int64_t)route * p.N;
-          if (p.out_peers != nullptr) {  // the row goes straight to the token's home GPU over NVLink
-            int64_t groute = route + p.route_offset;
-            if (groute >= p.total_routes) groute -= p.total_routes;
-            const int home = (int)(groute / p.routes_per_rank);
-            base = p.out_peers[home] + (groute - (int64_t)home * p.routes_per_rank) * p.N;
-          }
-          sh->dst[buf][tid] = (unsigned long long)(uintptr_t)base;
-          sh->wgt[buf][tid] = p.topk_w[route];
-        }
+      const int buf = tl & 1, rows = info.z, half = info.w;
+      // full form: lane = token rank*128 + lane, columns = weight rows; half form: lanes 0..63 hold tokens
+      // rank*64 + lane with weight rows 0..127, lanes 64..127 the same tokens with weight rows 128..255
+      const int tok = half ? rank * 64 + (q & 1) * 32 + lane : rank * TOK_ROWS + q * 32 + lane;
+      const int ncols = (half ? ITEM_N / 2 : ITEM_N) / CH;   // TMEM columns of this warp
+      const int col0 = hsel * ncols;
+      const int n_base = col0 + (half ? (q >> 1) * (ITEM_N / 2) : 0);  // item column behind TMEM column col0
+      const bool valid = tok < rows;
+      const int pos = info.y + (valid ? tok : 0);
+      // the item's per-column globals -> shared memory (one pass of the epilogue threads), then a (bounded) barrier
+      // among the epilogue threads: a table is rewritten two items later, after every warp has passed the next one
+      {
+        const float* gsrc = p.globals + (int64_t)info.x * (p.global_stride >> 2);
+        for (int c = tid; c < ITEM_N; c += EPI_WARPS * 32) sh->gl[buf][c] = gsrc[weight_row(wt, c)];
         mbar_arrive(smem_u32(&sh->table[buf]));
         if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&sh->table[buf]), (tl >> 1) & 1, abort_flag))) break;
       }
-      bool ok;
-#ifdef B200MOE_GG_PROFILE
-      ptab += clock64() - _tt0;
-#endif
-      {
-        PROF_T0
-        ok = mbar_wait(smem_u32(&sh->tmem_full[buf]), (tl >> 1) & 1, abort_flag);
-        PROF_ADD(pw)
+      float mul = 0.f;          // mode 0: inverse token scale; mode 1: router weight
+      char* dst = nullptr;      // first byte of this thread's outputs for item column n_base; null = no token here
+      if (MODE == 0) {
+        mul = p.a_inv[pos];
+        dst = reinterpret_cast<char*>(p.out) + ((int64_t)pos * p.half_n + wt * (ITEM_N / 2) + (n_base >> 1)) * 2;
+      } else {
+        const int route = p.sorted_routes[pos];
+        mul = p.topk_w[route];
+        __nv_bfloat16* base = reinterpret_cast<__nv_bfloat16*>(p.out) + (int64_t)route * p.N;
+        if (p.out_peers != nullptr) {  // the row goes straight to the token's home GPU over NVLink
+          int64_t groute = route + p.route_offset;
+          if (groute >= p.total_routes) groute -= p.total_routes;
+          const int home = (int)(groute / p.routes_per_rank);
+          base = p.out_peers[home] + (groute - (int64_t)home * p.routes_per_rank) * p.N;
+        }
+        dst = reinterpret_cast<char*>(base + wt * ITEM_N + n_base);
       }
-      ok = __all_sync(0xffffffffu, ok);
+      if (!valid) dst = nullptr;
+      // destinations of the four tokens of this lane's quad
+      char* dstq[4];
+#pragma unroll
+      for (int k = 0; k < 4; ++k)
+        dstq[k] = reinterpret_cast<char*>(__shfl_sync(0xffffffffu, (unsigned long long)(uintptr_t)dst, (lane & ~3) + k));
+      const bool ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&sh->tmem_full[buf]), (tl >> 1) & 1, abort_flag));
       if (!ok) break;
       tc_fence_after();
-#ifdef B200MOE_GG_PROFILE
-      const long long _tc0 = clock64();
-#endif
-      const uint32_t tbase = tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)(buf * TN);
-      // Both branches are written as straight-line code (every exchange first, then every address, then predicated
-      // stores): a warp issues in order, so a loop body that waits for its own shuffle or table read before it
-      // stores would expose that latency sixteen times per chunk.
-      auto finish = [&](const uint32_t (&v)[16], int c0) {
-        const int tok0 = c0 + (odd ? 8 : 0);
+      const uint32_t tbase = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * ITEM_N + col0);
+      const float* glt = &sh->gl[buf][n_base];
+      // one chunk = 16 TMEM columns of this thread's token -> NR registers of output
+      auto convert = [&](const uint32_t (&v)[16], int c, uint32_t (&o)[NR]) {
+        const float4* g4 = reinterpret_cast<const float4*>(glt + c);
         if (MODE == 0) {
-          // lanes 2i (gate) and 2i+1 (up) hold the same output column; the even lane finishes tokens c0..c0+7,
-          // the odd lane tokens c0+8..c0+15
-          float mine[16], got[8];
+          // columns 2i / 2i+1 = gate / up of output c/2 + i
+          float y[8];
 #pragma unroll
-          for (int j = 0; j < 16; ++j) mine[j] = bf16_round(__uint_as_float(v[j]) * g_mine);
-#pragma unroll
-          for (int j = 0; j < 8; ++j) got[j] = __shfl_xor_sync(0xffffffffu, odd ? mine[j] : mine[8 + j], 1);
-          __nv_bfloat16* dst = p.out + (int64_t)(info.y + tok0) * half_n + wt * 64 + (row >> 1);
-          unsigned short outv[8];
-#pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            const float gate = odd ? got[j] : mine[j];
-            const float up = odd ? mine[8 + j] : got[j];
-            outv[j] = __bfloat16_as_ushort(__float2bfloat16_rn(silu_mul(gate, up)));
+          for (int i = 0; i < 4; ++i) {
+            const float4 g = g4[i];  // gate, up, gate, up
+            const float gate0 = bf16_round((__uint_as_float(v[4 * i]) * mul) * g.x);
+            const float up0 = bf16_round((__uint_as_float(v[4 * i + 1]) * mul) * g.y);
+            const float gate1 = bf16_round((__uint_as_float(v[4 * i + 2]) * mul) * g.z);
+            const float up1 = bf16_round((__uint_as_float(v[4 * i + 3]) * mul) * g.w);
+            y[2 * i] = bf16_round(silu_mul(gate0, up0));
+            y[2 * i + 1] = bf16_round(silu_mul(gate1, up1));
           }
 #pragma unroll
-          for (int j = 0; j < 8; ++j)
-            asm volatile("{\n\t.reg .pred q;\n\tsetp.lt.s32 q, %2, %3;\n\t@q st.global.b16 [%0], %1;\n\t}"
-                         ::"l"(dst + (int64_t)j * half_n), "h"(outv[j]), "r"(tok0 + j), "r"(rows) : "memory");
+          for (int i = 0; i < 4; ++i) o[i] = pack_f16x2_sat(y[2 * i], y[2 * i + 1]);
         } else {
-          // neighbouring lanes own neighbouring output columns: the even lane stores both columns of tokens
-          // c0..c0+7, the odd lane both columns of tokens c0+8..c0+15 (4-byte stores, half as many of them)
-          float mine[16];
-          const float4* wq = reinterpret_cast<const float4*>(&sh->wgt[buf][c0]);
 #pragma unroll
-          for (int q = 0; q < 4; ++q) {
-            const float4 w4 = wq[q];
-            mine[4 * q + 0] = (__uint_as_float(v[4 * q + 0]) * g_mine) * w4.x;
-            mine[4 * q + 1] = (__uint_as_float(v[4 * q + 1]) * g_mine) * w4.y;
-            mine[4 * q + 2] = (__uint_as_float(v[4 * q + 2]) * g_mine) * w4.z;
-            mine[4 * q + 3] = (__uint_as_float(v[4 * q + 3]) * g_mine) * w4.w;
+          for (int i = 0; i < 4; ++i) {
+            const float4 g = g4[i];
+            o[2 * i] = pack_bf16x2((__uint_as_float(v[4 * i]) * g.x) * mul, (__uint_as_float(v[4 * i + 1]) * g.y) * mul);
+            o[2 * i + 1] = pack_bf16x2((__uint_as_float(v[4 * i + 2]) * g.z) * mul, (__uint_as_float(v[4 * i + 3]) * g.w) * mul);
           }
-          uint32_t outv[8];
-#pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            const float got = __shfl_xor_sync(0xffffffffu, odd ? mine[j] : mine[8 + j], 1);
-            outv[j] = odd ? pack_bf16x2(got, mine[8 + j]) : pack_bf16x2(mine[j], got);
-          }
-          unsigned long long d[8];
-#pragma unroll
-          for (int j = 0; j < 8; ++j) d[j] = sh->dst[buf][min(tok0 + j, TN - 1)] + (unsigned long long)(wrow & ~1) * 2;
-#pragma unroll
-          for (int j = 0; j < 8; ++j)
-            asm volatile("{\n\t.reg .pred q;\n\tsetp.lt.s32 q, %2, %3;\n\t@q st.global.b32 [%0], %1;\n\t}"
-                         ::"l"(d[j]), "r"(outv[j]), "r"(tok0 + j), "r"(rows) : "memory");
         }
       };
-      // two register sets: the next chunk's TMEM load is in flight while the current one is finished
-      uint32_t va[16], vb[16];
-      constexpr int CSTEP = (EPI_WARPS / 4) * 16;  // columns between two chunks of the same warp
-      int c0 = csel * 16;
-      if (c0 < npad) tc_ld16(tbase + c0, va);
+      // 64 columns at a time: four chunks, exchanged inside the quad so that lane j holds piece j of the outputs
+      // of each of the quad's four tokens; a store instruction then covers contiguous pieces of eight tokens
 #pragma unroll 1
-      for (; c0 < npad; c0 += 2 * CSTEP) {
-        tc_wait_ld();
-        if (c0 + CSTEP < npad) tc_ld16(tbase + c0 + CSTEP, vb);
-        finish(va, c0);
-        if (c0 + CSTEP < npad) {
+      for (int c = 0; c < ncols; c += 64) {
+        uint32_t blk[4][NR];
+        uint32_t v[16];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          tc_ld16(tbase + c + 16 * i, v);
           tc_wait_ld();
-          if (c0 + 2 * CSTEP < npad) tc_ld16(tbase + c0 + 2 * CSTEP, va);
-          finish(vb, c0 + CSTEP);
+          convert(v, c + 16 * i, blk[i]);
+        }
+        quad_transpose<NR>(blk, jq);
+        // bytes of 64 columns per token: 64 (mode 0, fp16 outputs of 32 pairs) or 128 (mode 1)
+        const int gbyte = MODE == 0 ? c : 2 * c;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          if (dstq[k] == nullptr) continue;
+          char* d = dstq[k] + gbyte + jq * (NR * 4);
+          stg_v4(d, make_uint4(blk[k][0], blk[k][1], blk[k][2], blk[k][3]));
+          if (NR == 8) stg_v4(d + 16, make_uint4(blk[k][NR - 4], blk[k][NR - 3], blk[k][NR - 2], blk[k][NR - 1]));
         }
       }
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) {
-        if (PAIR) mbar_arrive_cluster(leader(&sh->tmem_empty[buf]));
-        else mbar_arrive(smem_u32(&sh->tmem_empty[buf]));
-      }
-#ifdef B200MOE_GG_PROFILE
-      pchunk += clock64() - _tc0;
-#endif
+      if (lane == 0) mbar_arrive_cluster(leader(&sh->tmem_empty[buf]));
     }
-#ifdef B200MOE_GG_PROFILE
-    if (tid == 0) { g_gg_prof[MODE][blockIdx.x][12] = ptab; g_gg_prof[MODE][blockIdx.x][13] = pchunk; }
-    if (tid == 0) { g_gg_prof[MODE][blockIdx.x][0] = clock64() - ptot; g_gg_prof[MODE][blockIdx.x][1] = pw; g_gg_prof[MODE][blockIdx.x][2] = tl; }
-#endif
-  } else if (warp < TOK_WARP0) {
+  } else if (warp < R::TMA_A) {
     // ------------------------------------------------------------------ weight unpackers
-    // thread -> tile row wi*16 + lane/2, half `hf` of the stage's 64 k: 16 packed bytes and two block scales
-    const int dq = warp - EPI_WARPS, grp = dq / DQ_GROUP_WARPS, wi = dq % DQ_GROUP_WARPS;
-    const int a_row = wi * 16 + (lane >> 1), hf = lane & 1;
-    uint32_t a_dst[4];  // shared-memory offsets inside a stage never change: computed once
+    regs_give<R::REGS_UNPACK>();
+    // thread -> weight row `l` of this CTA's half of the item, all 64 k of a k-step: 32 packed bytes, four block scales
+    const int u = warp - R::UNPACK0, grp = u / GROUP_WARPS, l = (u % GROUP_WARPS) * 32 + lane;
+    const int j = rank * WROWS + l;  // row inside the item
+    const uint32_t b_row = l * 128, b_x = l & 7;
+    // unpacked row -> the k-step's B slot, then tell the relay
+    auto store_row = [&](uint32_t it, const uint4 (&c)[8]) -> bool {
+      const int s = it % SB;
+      if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&sh->empty_b[s]), ((it / SB) & 1) ^ 1, abort_flag))) return false;
+      const uint32_t sb = ring_b + s * B_BYTES + b_row;
 #pragma unroll
-    for (int c = 0; c < 4; ++c) a_dst[c] = a_row * 128 + (((hf * 4 + c) ^ (a_row & 7)) << 4);
-    // load cursor: (tile, kb) of the next weight bytes to request, four of this group's steps ahead of their use
-    int ltile = unit, lkb = grp;
-    const uint8_t *lprow = nullptr, *lsrow = nullptr;
-    auto place = [&]() {
-      if (ltile >= total_tiles) return;
-      const int tt = ltile / WPT, wt = PAIR ? 2 * (ltile - tt * WPT) + rank : ltile - tt * WPT;
-      const int slot = p.mtiles[tt].x;
-      int wrow;
-      if (MODE == 0) wrow = (a_row & 1) ? half_n + wt * 64 + (a_row >> 1) : wt * 64 + (a_row >> 1);
-      else wrow = wt * WM + a_row;
-      lprow = p.packed + (int64_t)slot * p.packed_stride + (int64_t)wrow * (p.K >> 1) + grp * 32 + hf * 16;
-      lsrow = p.scales + (int64_t)slot * p.scale_stride + (int64_t)wrow * (p.K >> 4) + grp * 4 + hf * 2;
+      for (int i = 0; i < 8; ++i) sts_v4(sb + ((i ^ b_x) << 4), c[i]);
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&sh->part[s]));
+      return true;
     };
-    place();
-    struct WRegs {
-      uint4 q;
-      uint32_t sc;
+    auto unpack_row = [&](const uint4& q0, const uint4& q1, uint32_t sc, uint4 (&c)[8]) {
+      const uint32_t s01 = e4m3x2_to_f16x2(sc & 0xffffu), s23 = e4m3x2_to_f16x2(sc >> 16);
+      const uint32_t sc0 = dup_lo16(s01), sc1 = dup_hi16(s01), sc2 = dup_lo16(s23), sc3 = dup_hi16(s23);
+      c[0] = unpack_chunk_f16(q0.x, sc0);
+      c[1] = unpack_chunk_f16(q0.y, sc0);
+      c[2] = unpack_chunk_f16(q0.z, sc1);
+      c[3] = unpack_chunk_f16(q0.w, sc1);
+      c[4] = unpack_chunk_f16(q1.x, sc2);
+      c[5] = unpack_chunk_f16(q1.y, sc2);
+      c[6] = unpack_chunk_f16(q1.z, sc3);
+      c[7] = unpack_chunk_f16(q1.w, sc3);
     };
-    auto fetch = [&](WRegs& r) {
-      if (ltile < total_tiles) {
-        r.q = ldg_nc_v4_l2line(lprow);
-        r.sc = ldg_nc_u16(lsrow);
-        lprow += 32 * DQ_GROUPS;
-        lsrow += 4 * DQ_GROUPS;
-        lkb += DQ_GROUPS;
-        if (lkb >= KB) {
-          lkb = grp;
-          ltile += units;
-          place();
-        }
-      }
-    };
-    WRegs r0{}, r1{}, r2{}, r3{}, r4{};
-    fetch(r0);
-    fetch(r1);
-    fetch(r2);
-    fetch(r3);
-    const float two112 = __uint_as_float(0x77800000u);
-    uint32_t it0 = 0;
-    bool ok = true;
-    long long pw = 0, ptot = clock64();
-    for (int tile = unit; tile < total_tiles && ok; tile += units, it0 += KB) {
-      for (int kb = grp; kb < KB; kb += DQ_GROUPS) {
-        const uint32_t it = it0 + kb;
-        fetch(r4);
-        const int s = it % STAGES;
-        bool w_ok;
-        {
-          PROF_T0
-          w_ok = mbar_wait(smem_u32(&sh->empty[s]), ((it / STAGES) & 1) ^ 1, abort_flag);
-          PROF_ADD(pw)
-        }
-        if (!__all_sync(0xffffffffu, w_ok)) {
-          ok = false;
-          break;
-        }
-        const uint32_t sa = ring_u32 + s * WSTAGE_BYTES;
-        const uint32_t sfu = e4m3x2_to_f16x2(r0.sc);
-        const float2 sf = __half22float2(*reinterpret_cast<const __half2*>(&sfu));
-        const float s_lo = sf.x * two112, s_hi = sf.y * two112;
-        const uint32_t sb0 = pack_bf16x2(s_lo, s_lo), sb1 = pack_bf16x2(s_hi, s_hi);
-        sts_v4(sa + a_dst[0], unpack_chunk(r0.q.x, sb0));
-        sts_v4(sa + a_dst[1], unpack_chunk(r0.q.y, sb0));
-        sts_v4(sa + a_dst[2], unpack_chunk(r0.q.z, sb1));
-        sts_v4(sa + a_dst[3], unpack_chunk(r0.q.w, sb1));
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    if (p.w_staged) {
+      // The packed bytes of four k-steps of every row sit in a staged block: rows in box order (gate_up: 64 gate
+      // rows, then 64 up rows), 128 bytes each, 16-byte chunks swizzled by the row; this group's k-step is chunk
+      // pair (2 grp, 2 grp + 1).  Scales: 16 bytes per row after the packed part, four per k-step.
+      const int tr = MODE == 0 ? ((l & 1) ? 64 + (l >> 1) : (l >> 1)) : l;
+      const uint32_t w_off0 = tr * 128 + (((2 * grp) ^ (tr & 7)) << 4), w_off1 = tr * 128 + (((2 * grp + 1) ^ (tr & 7)) << 4);
+      const uint32_t s_off = W_PACKED_BYTES + tr * 16 + grp * 4;
+      for (uint32_t it = grp; it < total_steps; it += GROUPS) {
+        const uint32_t blk = it / SUPER;
+        const int ws = blk % SW;
+        if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&sh->full_w[ws]), (blk / SW) & 1, abort_flag))) break;
+        const uint32_t wb = ring_w + ws * W_BYTES;
+        const uint4 q0 = lds_v4(wb + w_off0), q1 = lds_v4(wb + w_off1);
+        const uint32_t sc = lds_u32(wb + s_off);
+        uint4 c[8];
+        unpack_row(q0, q1, sc, c);
         __syncwarp();
-        if (lane == 0) mbar_arrive(smem_u32(PAIR ? &sh->part[s] : &sh->full[s]));
-        r0 = r1;
-        r1 = r2;
-        r2 = r3;
-        r3 = r4;
-      }
-    }
-#ifdef B200MOE_GG_PROFILE
-    if (lane == 0 && (dq == 0 || dq == DQ_GROUP_WARPS)) { g_gg_prof[MODE][blockIdx.x][3 + 2 * grp] = clock64() - ptot; g_gg_prof[MODE][blockIdx.x][4 + 2 * grp] = pw; }
-#endif
-  } else if (warp < RELAY_WARP) {
-    // ------------------------------------------------------------------ token rows (B operand)
-    long long pw = 0;
-    uint32_t it = 0;
-    bool ok = true;
-    if (MODE == 1) {
-      // ic2 rows are already in sorted order: one thread asks the TMA unit for 64-row boxes (its half of a pair's tile)
-      if (warp == TOK_WARP0 && lane == 0) {
-        for (int tile = unit; tile < total_tiles && ok; tile += units) {
-          const int4 info = p.mtiles[tile / WPT];
-          const int my_rows = PAIR ? info.w >> 1 : info.w;
-          const int row0 = info.y + rank * my_rows;
-          const int boxes = (my_rows + 63) >> 6;
-          for (int kb = 0; kb < KB; ++kb, ++it) {
-            const int s = it % STAGES;
-            {
-              PROF_T0
-              ok = mbar_wait(smem_u32(&sh->empty[s]), ((it / STAGES) & 1) ^ 1, abort_flag);
-              PROF_ADD(pw)
-            }
-            if (!ok) break;
-            const uint32_t sb = ring_u32 + s * WSTAGE_BYTES + WA_STAGE;
-            if (PAIR) {
-              const uint32_t bar = leader(&sh->full[s]);
-              if (rank == 0) mbar_arrive_expect_tx(smem_u32(&sh->full[s]), 2u * (uint32_t)boxes * (64u * 128u));
-              for (int b = 0; b < boxes; ++b) tma_load_2d_pair(sb + b * (64 * 128), &p.a_map, kb * BK, row0 + b * 64, bar);
-            } else {
-              const uint32_t bar = smem_u32(&sh->full[s]);
-              mbar_arrive_expect_tx(bar, (uint32_t)boxes * (64u * 128u));
-              for (int b = 0; b < boxes; ++b) tma_load_2d(sb + b * (64 * 128), &p.a_map, kb * BK, row0 + b * 64, bar);
-            }
-          }
-        }
+        if (lane == 0) mbar_arrive(smem_u32(&sh->empty_w[ws]));  // this warp holds its part of the block in registers
+        if (!store_row(it, c)) break;
       }
     } else {
-      // async copies issue slowly per warp (about 80 cycles each), so four warps share a stage's chunks:
-      // thread -> 16-byte chunk tt%8 of tile rows tt/8 + 16 i; row & 7 is the same for all of them, so is the swizzle
-      const int tt = tid - TOK_WARP0 * 32;
-      const int b_c = tt & 7, b_row0 = tt >> 3;
-      const uint32_t b_dst0 = WA_STAGE + b_row0 * 128 + ((b_c ^ (b_row0 & 7)) << 4);
-      constexpr int RSTEP = TOK_WARPS * 4, RPT = BROWS / RSTEP;  // row step, rows per thread
-      const char* abase = reinterpret_cast<const char*>(p.a);
-      for (int tile = unit; tile < total_tiles && ok; tile += units) {
-        const int4 info = p.mtiles[tile / WPT];
-        const int rows = info.z, my_rows = PAIR ? info.w >> 1 : info.w, row0 = rank * my_rows;
-        uint32_t boff[RPT];  // source of this thread's chunk of every row, in 16-byte units
-#pragma unroll
-        for (int i = 0; i < RPT; ++i) {
-          const int pos = info.y + min(row0 + b_row0 + RSTEP * i, rows - 1);
-          boff[i] = (uint32_t)(((int64_t)(p.sorted_routes[pos] / p.top_k) * p.lda) >> 3) + b_c;
+      // Reductions that are not a multiple of 256 (small test shapes): every thread reads its row from global memory,
+      // three of its steps ahead.  The loop is unrolled over the three register sets, so a set is only read again
+      // three steps after its loads were issued.
+      int l_item = unit, l_kb = grp;  // (item, k-step) of the next request
+      const uint8_t *lprow = nullptr, *lsrow = nullptr;
+      auto place = [&]() {
+        while (l_kb >= KB) {
+          l_kb -= KB;
+          l_item += units;
         }
-        for (int kb = 0; kb < KB; ++kb, ++it) {
-          const int s = it % STAGES;
-          bool w_ok;
-          {
-            PROF_T0
-            w_ok = mbar_wait(smem_u32(&sh->empty[s]), ((it / STAGES) & 1) ^ 1, abort_flag);
-            PROF_ADD(pw)
-          }
-          if (!__all_sync(0xffffffffu, w_ok)) {
-            ok = false;
-            break;
-          }
-          const uint32_t sb = ring_u32 + s * WSTAGE_BYTES + b_dst0;
-          const char* kbase = abase + kb * (BK * 2);
-#pragma unroll
-          for (int i = 0; i < RPT; ++i) {
-            if (b_row0 + RSTEP * i < my_rows)
-              asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(sb + i * (RSTEP * 128)), "l"(kbase + (uint64_t)boff[i] * 16) : "memory");
-          }
-          // a lone CTA's copies count on the stage's barrier themselves; in a pair they count on a local barrier
-          // that the relay thread forwards to the leader
-          cp_async_arrive_noinc(smem_u32(PAIR ? &sh->part[s] : &sh->full[s]));
+        if (l_item >= total_items) return;
+        const int tt = l_item / NT, wt = l_item - tt * NT;
+        const int slot = p.mtiles[tt].x;
+        const int wrow = weight_row(wt, j);
+        lprow = p.packed + (int64_t)slot * p.packed_stride + (int64_t)wrow * (p.K >> 1);
+        lsrow = p.scales + (int64_t)slot * p.scale_stride + (int64_t)wrow * (p.K >> 4);
+      };
+      place();
+      struct WRegs {
+        uint4 q0, q1;
+        uint32_t sc;
+      };
+      auto fetch = [&](WRegs& r) {
+        if (l_item < total_items) {
+          r.q0 = ldg_nc_v4_l2line(lprow + l_kb * 32);
+          r.q1 = ldg_nc_v4_l2line(lprow + l_kb * 32 + 16);
+          r.sc = ldg_nc_u32(lsrow + l_kb * 4);
+          l_kb += GROUPS;
+          if (l_kb >= KB) place();
         }
+      };
+      auto step = [&](WRegs& r, uint32_t it) -> bool {
+        uint4 c[8];
+        unpack_row(r.q0, r.q1, r.sc, c);
+        if (!store_row(it, c)) return false;
+        fetch(r);
+        return true;
+      };
+      WRegs r0{}, r1{}, r2{};
+      fetch(r0);
+      fetch(r1);
+      fetch(r2);
+      for (uint32_t it = grp; it < total_steps; it += 3 * GROUPS) {
+        if (!step(r0, it)) break;
+        if (it + GROUPS < total_steps && !step(r1, it + GROUPS)) break;
+        if (it + 2 * GROUPS < total_steps && !step(r2, it + 2 * GROUPS)) break;
       }
-      asm volatile("cp.async.wait_all;" ::: "memory");
     }
-#ifdef B200MOE_GG_PROFILE
-    if (tid == TOK_WARP0 * 32) g_gg_prof[MODE][blockIdx.x][7] = pw;
-#endif
-  } else if (warp < MMA_WARP) {
-    // ------------------------------------------------------------------ relay (pair): this CTA's part of a stage -> leader
-    // (no proxy fence here: the unpackers fenced their own stores, and a fence in this thread costs more than a
-    // k-step of MMA)
+  } else {
+   regs_give<R::REGS_MISC>();  // the four single-thread roles form one warpgroup
+   if (warp == R::TMA_A) {
+    // ------------------------------------------------------------------ token rows (A operand)
     if (lane == 0) {
       uint32_t it = 0;
       bool ok = true;
-      const uint32_t leader_full = leader(&sh->full[0]);
-      for (int tile = unit; tile < total_tiles && ok; tile += units) {
+      int4 info_next = unit < total_items ? p.mtiles[unit / NT] : make_int4(0, 0, 0, 0);
+      for (int item = unit; item < total_items && ok; item += units) {
+        const int4 info = info_next;
+        if (item + units < total_items) info_next = p.mtiles[(item + units) / NT];  // needed one item from now
+        const int half = info.w;
+        const int row0 = info.y + rank * (half ? 64 : TOK_ROWS);
+        const int boxes = half ? 1 : 2;
         for (int kb = 0; kb < KB; ++kb, ++it) {
-          const int s = it % STAGES;
-          if (!mbar_wait<0>(smem_u32(&sh->part[s]), (it / STAGES) & 1, abort_flag)) {
-            ok = false;
-            break;
-          }
-          mbar_arrive_cluster(leader_full + s * 8);
+          const int s = it % SA;
+          ok = mbar_wait(smem_u32(&sh->empty_a[s]), ((it / SA) & 1) ^ 1, abort_flag);
+          if (!ok) break;
+          const uint32_t sa = ring_a + s * A_BYTES;
+          const uint32_t bar = leader(&sh->full_a[s]);
+          if (rank == 0) mbar_arrive_expect_tx(smem_u32(&sh->full_a[s]), 2u * (uint32_t)boxes * (64u * 128u));
+          for (int b = 0; b < boxes; ++b) tma_load_2d_pair(sa + b * (64 * 128), &p.a_map, kb * BK, row0 + b * 64, bar);
         }
+      }
+    }
+  } else if (warp == R::TMA_W) {
+    // ------------------------------------------------------------------ packed weights -> staging ring
+    if (lane == 0 && p.w_staged) {
+      uint32_t blk = 0;
+      bool ok = true;
+      int slot_next = unit < total_items ? p.mtiles[unit / NT].x : 0;
+      const int blocks = KB / SUPER;
+      for (int item = unit; item < total_items && ok; item += units) {
+        const int slot = slot_next, wt = item % NT;
+        if (item + units < total_items) slot_next = p.mtiles[(item + units) / NT].x;  // needed one item from now
+        // first row of the two 64-row boxes of this CTA's half of the item
+        int row_a, row_b;
+        if (MODE == 0) {
+          row_a = wt * (ITEM_N / 2) + 64 * rank;
+          row_b = p.half_n + row_a;
+        } else {
+          row_a = wt * ITEM_N + WROWS * rank;
+          row_b = row_a + 64;
+        }
+        for (int ss = 0; ss < blocks; ++ss, ++blk) {
+          const int ws = blk % SW;
+          ok = mbar_wait(smem_u32(&sh->empty_w[ws]), ((blk / SW) & 1) ^ 1, abort_flag);
+          if (!ok) break;
+          const uint32_t wb = ring_w + ws * W_BYTES, bar = smem_u32(&sh->full_w[ws]);
+          mbar_arrive_expect_tx(bar, (uint32_t)W_BYTES);
+          tma_load_3d(wb, &p.w_map, ss * (SUPER * BK / 2), row_a, slot, bar);
+          tma_load_3d(wb + W_PACKED_BYTES / 2, &p.w_map, ss * (SUPER * BK / 2), row_b, slot, bar);
+          tma_load_3d(wb + W_PACKED_BYTES, &p.s_map, ss * (SUPER * BK / 16), row_a, slot, bar);
+          tma_load_3d(wb + W_PACKED_BYTES + W_SCALE_BYTES / 2, &p.s_map, ss * (SUPER * BK / 16), row_b, slot, bar);
+        }
+      }
+    }
+  } else if (warp == R::RELAY) {
+    // ------------------------------------------------------------------ relay: this CTA's weight half of a k-step -> leader
+    // (no proxy fence here: the unpackers fenced their own stores)
+    if (lane == 0) {
+      const uint32_t leader_full = leader(&sh->full_b[0]);
+      for (uint32_t it = 0; it < total_steps; ++it) {
+        const int s = it % SB;
+        if (!mbar_wait(smem_u32(&sh->part[s]), (it / SB) & 1, abort_flag)) break;
+        mbar_arrive_cluster(leader_full + s * 8);
       }
     }
   } else {
     // ------------------------------------------------------------------ MMA issuer (the pair's leader only)
     if (lane == 0 && rank == 0) {
-      // This thread is the only one that feeds the tensor pipe, and it shares a scheduler with six busy warps:
-      // every instruction here can cost several cycles of an idle pipe, so stage index, barrier addresses, wait
-      // parity and operand descriptors are carried along instead of being recomputed from a step counter.
       int tl = 0;
       bool ok = true;
-      long long pwf = 0, pwt = 0, ptot = clock64(), pn = 0, pmma = 0, pcommit = 0;
-      int s = 0;
-      uint32_t phase = 0;
-      const uint32_t full0 = smem_u32(&sh->full[0]), empty0 = smem_u32(&sh->empty[0]);
-      const uint64_t ad0 = umma_desc_sw128(ring_u32), bd0 = umma_desc_sw128(ring_u32 + WA_STAGE);
-      constexpr uint64_t STAGE_UNITS = WSTAGE_BYTES >> 4;  // descriptor start addresses count 16-byte units
+      int sa = 0, sb = 0;
+      uint32_t phase_a = 0, phase_b = 0;
+      const uint32_t full_a0 = smem_u32(&sh->full_a[0]), empty_a0 = smem_u32(&sh->empty_a[0]);
+      const uint32_t full_b0 = smem_u32(&sh->full_b[0]), empty_b0 = smem_u32(&sh->empty_b[0]);
+      const uint64_t ad0 = umma_desc_sw128(ring_a), bd0 = umma_desc_sw128(ring_b);
+      constexpr uint64_t SLOT_UNITS = A_BYTES >> 4;  // descriptor start addresses count 16-byte units
       uint64_t ad = ad0, bd = bd0;
-      for (int tile = unit; tile < total_tiles && ok; tile += units, ++tl) {
-        const int npad = p.mtiles[tile / WPT].w;
-        pn += npad;
-        const uint32_t idesc = umma_idesc_n(npad, PAIR ? 2 * WM : WM);
+      int half_next = unit < total_items ? p.mtiles[unit / NT].w : 0;
+      for (int item = unit; item < total_items && ok; item += units, ++tl) {
+        const int half = half_next;
+        if (item + units < total_items) half_next = p.mtiles[(item + units) / NT].w;  // needed one item from now
+        const uint32_t idesc = umma_idesc_f16(ITEM_N, half ? TOK_ROWS : 2 * TOK_ROWS);
         const int buf = tl & 1;
-        {
-          PROF_T0
-          const bool w_ok = mbar_wait<0>(smem_u32(&sh->tmem_empty[buf]), ((tl >> 1) & 1) ^ 1, abort_flag);
-          PROF_ADD(pwt)
-          if (!w_ok) break;
-        }
+        if (!mbar_wait(smem_u32(&sh->tmem_empty[buf]), ((tl >> 1) & 1) ^ 1, abort_flag)) break;
         tc_fence_after();
-        const uint32_t d = tmem_base + (uint32_t)(buf * TN);
+        const uint32_t d = tmem_base + (uint32_t)(buf * ITEM_N);
         for (int kb = 0; kb < KB; ++kb) {
-          {
-            PROF_T0
-            const bool w_ok = mbar_wait<0>(full0 + 8 * s, phase, abort_flag);
-            PROF_ADD(pwf)
-            if (!w_ok) {
-              ok = false;
-              break;
-            }
+          if (!mbar_wait(full_b0 + 8 * sb, phase_b, abort_flag) || !mbar_wait(full_a0 + 8 * sa, phase_a, abort_flag)) {
+            ok = false;
+            break;
           }
           tc_fence_after();
-#ifdef B200MOE_GG_PROFILE
-          const long long _m0 = clock64();
-#endif
-          if (PAIR) {
-            tc_mma_f16_pair(d, ad, bd, idesc, kb != 0);
-            tc_mma_f16_pair(d, ad + 2, bd + 2, idesc, 1);
-            tc_mma_f16_pair(d, ad + 4, bd + 4, idesc, 1);
-            tc_mma_f16_pair(d, ad + 6, bd + 6, idesc, 1);
-#ifdef B200MOE_GG_PROFILE
-            const long long _m1 = clock64();
-            pmma += _m1 - _m0;
-#endif
-            tc_commit_pair(empty0 + 8 * s, 3);
-#ifdef B200MOE_GG_PROFILE
-            pcommit += clock64() - _m1;
-#endif
-          } else {
-            tc_mma_f16(d, ad, bd, idesc, kb != 0);
-            tc_mma_f16(d, ad + 2, bd + 2, idesc, 1);
-            tc_mma_f16(d, ad + 4, bd + 4, idesc, 1);
-            tc_mma_f16(d, ad + 6, bd + 6, idesc, 1);
-            tc_commit(empty0 + 8 * s);
-          }
-          if (++s == STAGES) {
-            s = 0;
-            phase ^= 1;
+          tc_mma_f16_pair(d, ad, bd, idesc, kb != 0);
+          tc_mma_f16_pair(d, ad + 2, bd + 2, idesc, 1);
+          tc_mma_f16_pair(d, ad + 4, bd + 4, idesc, 1);
+          tc_mma_f16_pair(d, ad + 6, bd + 6, idesc, 1);
+          tc_commit_pair(empty_a0 + 8 * sa, 3);
+          tc_commit_pair(empty_b0 + 8 * sb, 3);
+          if (++sa == SA) {
+            sa = 0;
+            phase_a ^= 1;
             ad = ad0;
+          } else {
+            ad += SLOT_UNITS;
+          }
+          if (++sb == SB) {
+            sb = 0;
+            phase_b ^= 1;
             bd = bd0;
           } else {
-            ad += STAGE_UNITS;
-            bd += STAGE_UNITS;
+            bd += SLOT_UNITS;
           }
         }
-        if (ok) {
-          if (PAIR) tc_commit_pair(smem_u32(&sh->tmem_full[buf]), 3);
-          else tc_commit(smem_u32(&sh->tmem_full[buf]));
-        }
+        if (ok) tc_commit_pair(smem_u32(&sh->tmem_full[buf]), 3);
       }
-#ifdef B200MOE_GG_PROFILE
-      g_gg_prof[MODE][blockIdx.x][8] = clock64() - ptot; g_gg_prof[MODE][blockIdx.x][9] = pwf; g_gg_prof[MODE][blockIdx.x][10] = pwt; g_gg_prof[MODE][blockIdx.x][11] = pn; g_gg_prof[MODE][blockIdx.x][14] = pmma; g_gg_prof[MODE][blockIdx.x][15] = pcommit;
-#endif
     }
     __syncwarp();
+   }
   }
 
   tc_fence_before();
   __syncthreads();
   if (tid == 0 && sh->abort_flag) atomicExch(p.status, 11 + MODE);
-  if (PAIR) cluster_sync_all();  // neither CTA frees its TMEM or leaves while the other may still use its memory
-  if (warp == MMA_WARP) {
+  cluster_sync_all();  // neither CTA frees its TMEM or leaves while the other may still use its memory
+  if (warp == R::MMA) {
     tc_fence_after();
-    if (PAIR) asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)TMEM_COLS) : "memory");
-    else asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)TMEM_COLS) : "memory");
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)TMEM_COLS) : "memory");
   }
 }
 
-// Token-tile list of the grouped GEMM: {slot, first sorted position, rows <= 256, rows rounded up to 32 (each CTA
-// of a pair holds half of them, a multiple of 16)}.
-// Full tiles first, partial tiles after them, so that the static round-robin hands every CTA a similar mix.
+// Token-tile list of the grouped GEMM: {slot, first sorted position, rows <= 256, half}.  half = 1: at most 128
+// rows, run as M = 128 over the pair.  Full tiles first, then the 129..255-row tiles, then the half tiles, so that
+// the static round-robin hands every CTA pair a similar mix.
 __global__ void __launch_bounds__(1024) build_ttiles_kernel(const int32_t* __restrict__ offsets, int num_slots,
                                                             int4* __restrict__ tiles, int32_t* __restrict__ num_tiles) {
-  // thread e: expert e (num_slots <= 1024).  Exclusive scans of the full-tile and partial-tile counts over the
-  // experts: warp shuffles, then the warp totals.
-  __shared__ int32_t wfull[32], wpart[32];
+  // thread e: expert e (num_slots <= 1024).  Exclusive scans of the three tile counts over the experts: warp
+  // shuffles, then the warp totals.
+  __shared__ int32_t wtot[3][32];
   const int e = threadIdx.x, lane = e & 31, warp = e >> 5;
   int begin = 0, cnt = 0;
   if (e < num_slots) {
     begin = offsets[e];
     cnt = offsets[e + 1] - begin;
   }
-  const int nf = cnt / TN, np = (cnt % TN) != 0;
-  int sf = nf, sp = np;  // inclusive scans inside the warp
+  const int rem = cnt % TN;
+  const int n[3] = {cnt / TN, rem > TN / 2 ? 1 : 0, (rem > 0 && rem <= TN / 2) ? 1 : 0};
+  int sc[3] = {n[0], n[1], n[2]};  // inclusive scans inside the warp
 #pragma unroll
   for (int o = 1; o < 32; o <<= 1) {
-    const int a = __shfl_up_sync(0xffffffffu, sf, o), b = __shfl_up_sync(0xffffffffu, sp, o);
-    if (lane >= o) {
-      sf += a;
-      sp += b;
+#pragma unroll
+    for (int c = 0; c < 3; ++c) {
+      const int a = __shfl_up_sync(0xffffffffu, sc[c], o);
+      if (lane >= o) sc[c] += a;
     }
   }
-  if (lane == 31) {
-    wfull[warp] = sf;
-    wpart[warp] = sp;
-  }
+  if (lane == 31)
+    for (int c = 0; c < 3; ++c) wtot[c][warp] = sc[c];
   __syncthreads();
-  int bf = 0, bp = 0, tf = 0;
-  for (int w = 0; w < 32; ++w) {
-    if (w < warp) {
-      bf += wfull[w];
-      bp += wpart[w];
+  int before[3] = {0, 0, 0}, total[3] = {0, 0, 0};
+  for (int w = 0; w < 32; ++w)
+    for (int c = 0; c < 3; ++c) {
+      if (w < warp) before[c] += wtot[c][w];
+      total[c] += wtot[c][w];
     }
-    tf += wfull[w];
-  }
-  const int full_off = bf + sf - nf, part_off = bp + sp - np, nfull = tf;
-  if (e == 1023) *num_tiles = nfull + bp + sp;  // the last thread holds the inclusive totals
+  if (e == 0) *num_tiles = total[0] + total[1] + total[2];
   if (e < num_slots) {
-    int o = full_off;
-    for (int i = 0; i < nf; ++i, ++o) tiles[o] = make_int4(e, begin + i * TN, TN, TN);
-    const int rem = cnt % TN;
-    if (rem) tiles[nfull + part_off] = make_int4(e, begin + cnt - rem, rem, (rem + 31) & ~31);
+    int o = before[0] + sc[0] - n[0];
+    for (int i = 0; i < n[0]; ++i, ++o) tiles[o] = make_int4(e, begin + i * TN, TN, 0);
+    if (n[1]) tiles[total[0] + before[1] + sc[1] - 1] = make_int4(e, begin + cnt - rem, rem, 0);
+    if (n[2]) tiles[total[0] + total[1] + before[2] + sc[2] - 1] = make_int4(e, begin + cnt - rem, rem, 1);
+  }
+}
+
+// Token rows in expert order for the gate_up GEMM: xs[pos] = fp16(x[token of the route at sorted position pos] *
+// 2^s), s chosen per row so that the largest element lands just under the fp16 range (exact for bf16 inputs unless
+// an element is 2^28 below the row maximum), inv[pos] = 2^-s.  One warp per row; the rows may live on another GPU
+// (expert parallel: `src_peers` holds every rank's token buffer, peer-mapped; plain loads).
+__global__ void __launch_bounds__(256) gather_rows_f16_kernel(const __nv_bfloat16* __restrict__ x, int64_t lda,
+                                                              const __nv_bfloat16* const* __restrict__ src_peers,
+                                                              int tokens_per_rank, const int32_t* __restrict__ sorted_routes,
+                                                              const int32_t* __restrict__ offsets, int num_slots, int top_k,
+                                                              int H, __half* __restrict__ xs, float* __restrict__ inv_out) {
+  const int lane = threadIdx.x & 31;
+  const int64_t pos = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  if (pos >= offsets[num_slots]) return;
+  const int token = sorted_routes[pos] / top_k;
+  const __nv_bfloat16* row;
+  if (src_peers != nullptr) row = src_peers[token / tokens_per_rank] + (int64_t)(token % tokens_per_rank) * lda;
+  else row = x + (int64_t)token * lda;
+  __half* dst = xs + pos * H;
+  // rows up to 2048 elements stay in registers between the two passes; longer rows are read twice
+  uint4 v[8];
+  float amax = 0.f;
+  for (int k0 = 0; k0 < H; k0 += 2048) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int k = k0 + (i * 32 + lane) * 8;
+      v[i] = make_uint4(0, 0, 0, 0);
+      if (k < H) v[i] = ldg_nc_v4(row + k);
+      const uint32_t w[4] = {v[i].x, v[i].y, v[i].z, v[i].w};
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        amax = fmaxf(amax, fabsf(bf16_bits_to_float(w[c] & 0xffffu)));
+        amax = fmaxf(amax, fabsf(__uint_as_float(w[c] & 0xffff0000u)));
+      }
+    }
+  }
+  amax = warp_max(amax);
+  float scale, inv;
+  f16_row_scale(amax, scale, inv);
+  if (lane == 0) inv_out[pos] = inv;
+  for (int k0 = 0; k0 < H; k0 += 2048) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int k = k0 + (i * 32 + lane) * 8;
+      if (k >= H) continue;
+      if (H > 2048) v[i] = ldg_nc_v4(row + k);
+      const uint32_t w[4] = {v[i].x, v[i].y, v[i].z, v[i].w};
+      uint32_t o[4];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        const __half2 h = __floats2half2_rn(bf16_bits_to_float(w[c] & 0xffffu) * scale, __uint_as_float(w[c] & 0xffff0000u) * scale);
+        o[c] = *reinterpret_cast<const uint32_t*>(&h);
+      }
+      *reinterpret_cast<uint4*>(dst + k) = make_uint4(o[0], o[1], o[2], o[3]);
+    }
   }
 }
 
@@ -904,7 +879,9 @@ struct PrefillWs {
   int64_t perm_bytes;
   int32_t *sorted_routes, *offsets, *num_mtiles;
   int4* mtiles;
-  __nv_bfloat16 *ic2, *ic3;
+  __half *xs, *ic2;
+  float* a_inv;
+  __nv_bfloat16* ic3;
   int64_t bytes;
 };
 static PrefillWs carve_prefill_ws(void* ws, int T, int top_k, int H, int I, int slots) {
@@ -919,33 +896,58 @@ static PrefillWs carve_prefill_ws(void* ws, int T, int top_k, int H, int I, int 
   w.offsets = reinterpret_cast<int32_t*>(p + off); off += up(((int64_t)slots + 2) * 4);
   w.num_mtiles = reinterpret_cast<int32_t*>(p + off); off += up(16);
   w.mtiles = reinterpret_cast<int4*>(p + off); off += up((R / TN + slots + 2) * 16);
-  w.ic2 = reinterpret_cast<__nv_bfloat16*>(p + off); off += up((R + TN) * I * 2);
+  w.a_inv = reinterpret_cast<float*>(p + off); off += up((R + TN) * 4);
+  w.xs = reinterpret_cast<__half*>(p + off); off += up((R + TN) * H * 2);
+  w.ic2 = reinterpret_cast<__half*>(p + off); off += up((R + TN) * I * 2);
   w.ic3 = reinterpret_cast<__nv_bfloat16*>(p + off); off += up(R * H * 2);
   w.bytes = off;
   return w;
 }
 
-// Tensor map of a row-major bf16 matrix [rows, cols] (row pitch in elements): boxes of 64 columns x 64 rows,
+// Tensor map of a row-major fp16 matrix [rows, cols] (row pitch in elements): boxes of 64 columns x 64 rows,
 // 128-byte swizzle.  The encoder lives in the driver; it is looked up once.
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static std::mutex g_prefill_lock;
+static EncodeTiledFn g_encode_tiled = nullptr;
 static int encode_rows_map(CUtensorMap* map, const void* base, int64_t rows, int64_t cols, int64_t pitch) {
-  static EncodeTiledFn encode = nullptr;
-  if (!encode) {
-    void* fn = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q);
-    if (e != cudaSuccess) return (int)e;
-    if (!fn || q != cudaDriverEntryPointSuccess) return B200MOE_E_DEVICE;
-    encode = reinterpret_cast<EncodeTiledFn>(fn);
+  EncodeTiledFn& encode = g_encode_tiled;
+  {
+    std::lock_guard<std::mutex> guard(g_prefill_lock);
+    if (!encode) {
+      void* fn = nullptr;
+      cudaDriverEntryPointQueryResult q;
+      cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q);
+      if (e != cudaSuccess) return (int)e;
+      if (!fn || q != cudaDriverEntryPointSuccess) return B200MOE_E_DEVICE;
+      encode = reinterpret_cast<EncodeTiledFn>(fn);
+    }
   }
   const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
   const cuuint64_t strides[1] = {(cuuint64_t)pitch * 2};
   const cuuint32_t box[2] = {(cuuint32_t)BK, 64}, elem[2] = {1, 1};
-  const CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+  const CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
                             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : B200MOE_E_ALIGN;
+}
+
+// Tensor map of a bank role seen as bytes [slots, rows, row_bytes] (row pitch = row_bytes, slot pitch given):
+// boxes of box_bytes x 64 rows x 1 slot.
+static int encode_bank_map(CUtensorMap* map, const void* base, int64_t slots, int64_t rows, int64_t row_bytes,
+                           int64_t slot_pitch, int box_bytes, bool swizzle128) {
+  CUtensorMap probe;
+  if (int rc = encode_rows_map(&probe, base, 64, 64, 64)) {  // makes sure the encoder has been looked up
+    if (rc != B200MOE_E_ALIGN) return rc;
+  }
+  const cuuint64_t dims[3] = {(cuuint64_t)row_bytes, (cuuint64_t)rows, (cuuint64_t)slots};
+  const cuuint64_t strides[2] = {(cuuint64_t)row_bytes, (cuuint64_t)slot_pitch};
+  const cuuint32_t box[3] = {(cuuint32_t)box_bytes, 64, 1}, elem[3] = {1, 1, 1};
+  const CUresult r = g_encode_tiled(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void*>(base), dims, strides, box, elem,
+                                    CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                    swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                                    CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? 0 : B200MOE_E_ALIGN;
 }
 
@@ -953,24 +955,18 @@ static int encode_rows_map(CUtensorMap* map, const void* base, int64_t rows, int
 
 using namespace b200moe;
 
-#ifdef B200MOE_GG_PROFILE
-extern "C" int b200moe_debug_gg_profile(long long* host_out) {
-  return (int)cudaMemcpyFromSymbol(host_out, g_gg_prof, sizeof(long long) * 2 * 160 * 16);
-}
-#endif
-
 extern "C" int64_t b200moe_prefill_workspace_bytes(int T, int top_k, int hidden, int intermediate, int num_slots) {
   if (T < 0 || top_k < 1 || num_slots < 1) return 0;
   return carve_prefill_ws(nullptr, T, top_k, hidden, intermediate, num_slots).bytes;
 }
 
-// One grouped GEMM launch: `units` lone CTAs, or `units` clusters of two CTAs.
-template <int MODE, bool PAIR>
+// One grouped GEMM launch: `units` clusters of two CTAs.
+template <int MODE>
 static int launch_grouped_gemm(const GgParams& g, int units, cudaStream_t st) {
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(PAIR ? 2 * units : units);
-  cfg.blockDim = dim3(Roles<MODE, PAIR>::THREADS);
-  cfg.dynamicSmemBytes = WS_SMEM;
+  cfg.gridDim = dim3(2 * units);
+  cfg.blockDim = dim3(Roles<MODE>::THREADS);
+  cfg.dynamicSmemBytes = GG_SMEM;
   cfg.stream = st;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -978,19 +974,18 @@ static int launch_grouped_gemm(const GgParams& g, int units, cudaStream_t st) {
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = PAIR ? 1 : 0;
-  const cudaError_t e = cudaLaunchKernelEx(&cfg, grouped_gemm_ws_kernel<MODE, PAIR>, g);
+  cfg.numAttrs = 1;
+  const cudaError_t e = cudaLaunchKernelEx(&cfg, grouped_gemm_kernel<MODE>, g);
   return e == cudaSuccess ? 0 : (int)e;
 }
 
-// How many CTA pairs of the grouped GEMM can be resident at once (0: run lone CTAs).  The environment variable
-// B200MOE_GG_PAIR=0 forces lone CTAs (a diagnostic switch for comparing the two forms).
+// How many CTA pairs of the grouped GEMM can be resident at once.
 template <int MODE>
 static int resident_pairs(int sm_count) {
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(2 * (sm_count / 2));
-  cfg.blockDim = dim3(Roles<MODE, true>::THREADS);
-  cfg.dynamicSmemBytes = WS_SMEM;
+  cfg.blockDim = dim3(Roles<MODE>::THREADS);
+  cfg.dynamicSmemBytes = GG_SMEM;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = 2;
@@ -999,11 +994,42 @@ static int resident_pairs(int sm_count) {
   cfg.attrs = attr;
   cfg.numAttrs = 1;
   int n = 0;
-  if (cudaOccupancyMaxActiveClusters(&n, grouped_gemm_ws_kernel<MODE, true>, &cfg) != cudaSuccess) {
+  if (cudaOccupancyMaxActiveClusters(&n, grouped_gemm_kernel<MODE>, &cfg) != cudaSuccess) {
     cudaGetLastError();
     return 0;
   }
   return n;
+}
+
+// Launch state that belongs to a device (function attributes and the occupancy result are per device): looked up
+// once per device ordinal under a lock.
+struct PrefillDevice {
+  bool ready = false;
+  int pairs = 0;
+};
+static PrefillDevice g_prefill_dev[64];
+
+static int prefill_device_state(int* pairs) {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return (int)e;
+  if (dev < 0 || dev >= 64) return B200MOE_E_DEVICE;
+  std::lock_guard<std::mutex> guard(g_prefill_lock);
+  PrefillDevice& d = g_prefill_dev[dev];
+  if (!d.ready) {
+    cudaDeviceProp prop;
+    e = cudaGetDeviceProperties(&prop, dev);
+    if (e != cudaSuccess) return (int)e;
+    if (prop.major != 10) return B200MOE_E_DEVICE;
+    e = cudaFuncSetAttribute(grouped_gemm_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GG_SMEM);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(grouped_gemm_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GG_SMEM);
+    if (e != cudaSuccess) return (int)e;
+    d.pairs = std::min(resident_pairs<0>(prop.multiProcessorCount), resident_pairs<1>(prop.multiProcessorCount));
+    if (d.pairs < 1) return B200MOE_E_DEVICE;
+    d.ready = true;
+  }
+  *pairs = d.pairs;
+  return 0;
 }
 
 static int prefill_stages_impl(const void* x, const b200moe_banks* banks, const float* topk_weights,
@@ -1016,14 +1042,14 @@ static int prefill_stages_impl(const void* x, const b200moe_banks* banks, const 
       !banks->down_scale || !banks->down_global || !x || !topk_weights || !topk_ids || !out || !workspace || !status)
     return B200MOE_E_NULL;
   const int H = banks->hidden, I = banks->intermediate, S = banks->num_slots;
-  // H, I multiples of 128: the two unpack groups alternate 64-k steps, so there must be an even number of them
-  if (T < 0 || top_k < 1 || S < 1 || S > 1024 || H % WM || I % 64 || H % (2 * BK) || I % (2 * BK) ||
+  // an item is 256 weight rows: 128 gate + 128 up rows of gate_up, 256 rows of down; stages are 64 k wide
+  if (T < 0 || top_k < 1 || S < 1 || S > 1024 || H % ITEM_N || I % (ITEM_N / 2) || H % BK || I % BK ||
       (int64_t)T * top_k > (1ll << 30))
     return B200MOE_E_SHAPE;
   if ((shared == nullptr) != (shared_gate_logit == nullptr)) return B200MOE_E_NULL;
   if (!aligned16(x) || !aligned16(out) || !aligned16(workspace) || !aligned16(banks->gate_up) ||
-      !aligned16(banks->down) || (reinterpret_cast<uintptr_t>(banks->gate_up_scale) & 3) ||
-      (reinterpret_cast<uintptr_t>(banks->down_scale) & 3) || (shared && !aligned16(shared)))
+      !aligned16(banks->down) || !aligned16(banks->gate_up_scale) || !aligned16(banks->down_scale) || (reinterpret_cast<uintptr_t>(banks->gate_up_global) & 15) ||
+      (reinterpret_cast<uintptr_t>(banks->down_global) & 15) || (shared && !aligned16(shared)))
     return B200MOE_E_ALIGN;
   PrefillWs ws = carve_prefill_ws(workspace, T, top_k, H, I, S);
   if (workspace_bytes < ws.bytes) return B200MOE_E_WORKSPACE;
@@ -1033,30 +1059,14 @@ static int prefill_stages_impl(const void* x, const b200moe_banks* banks, const 
     if (nrc) return nrc;
     banks = &nb;
   }
+  // the epilogue reads the per-row globals as 16-byte vectors
+  if ((banks->slot_stride[2] & 15) || (banks->slot_stride[5] & 15)) return B200MOE_E_ALIGN;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   const int R = T * top_k;
+  int pairs = 0;
+  int rc = prefill_device_state(&pairs);
+  if (rc) return rc;
 
-  static int sm_count = 0, pairs = 0;
-  static bool attr_done = false;
-  if (!attr_done) {
-    int dev = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceProp prop;
-    cudaError_t e = cudaGetDeviceProperties(&prop, dev);
-    if (e != cudaSuccess) return (int)e;
-    if (prop.major != 10) return B200MOE_E_DEVICE;
-    sm_count = prop.multiProcessorCount;
-    e = cudaFuncSetAttribute(grouped_gemm_ws_kernel<0, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)WS_SMEM);
-    if (e == cudaSuccess) e = cudaFuncSetAttribute(grouped_gemm_ws_kernel<1, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)WS_SMEM);
-    if (e == cudaSuccess) e = cudaFuncSetAttribute(grouped_gemm_ws_kernel<0, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)WS_SMEM);
-    if (e == cudaSuccess) e = cudaFuncSetAttribute(grouped_gemm_ws_kernel<1, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)WS_SMEM);
-    if (e != cudaSuccess) return (int)e;
-    const char* env = getenv("B200MOE_GG_PAIR");
-    pairs = (env && env[0] == '0') ? 0 : std::min(resident_pairs<0>(sm_count), resident_pairs<1>(sm_count));
-    if (pairs < sm_count / 4) pairs = 0;  // too few co-resident clusters: lone CTAs use the machine better
-    attr_done = true;
-  }
-  int rc = 0;
   if (stage_mask & B200MOE_STAGE_PLAN) {
     cudaError_t ce = cudaMemsetAsync(status, 0, 4 * sizeof(int32_t), st);
     if (ce != cudaSuccess) return (int)ce;
@@ -1065,12 +1075,20 @@ static int prefill_stages_impl(const void* x, const b200moe_banks* banks, const 
     if (rc) return rc;
     build_ttiles_kernel<<<1, 1024, 0, st>>>(ws.offsets, S, ws.mtiles, ws.num_mtiles);
     if ((rc = check_launch())) return rc;
+    gather_rows_f16_kernel<<<(unsigned)(((int64_t)R * 32 + 255) / 256), 256, 0, st>>>(
+        reinterpret_cast<const __nv_bfloat16*>(x), H, nullptr, 1, ws.sorted_routes, ws.offsets, S, top_k, H, ws.xs, ws.a_inv);
+    if ((rc = check_launch())) return rc;
   }
 
   const int max_mtiles = R / TN + S;  // token tiles: full ones plus at most one partial per slot
   GgParams g1{};
-  g1.a = reinterpret_cast<const __nv_bfloat16*>(x);
-  g1.lda = H;
+  if ((rc = encode_rows_map(&g1.a_map, ws.xs, (int64_t)R + TN, H, H))) return rc;
+  const bool staged1 = H % (SUPER * BK) == 0, staged2 = I % (SUPER * BK) == 0;
+  if (staged1) {
+    if ((rc = encode_bank_map(&g1.w_map, banks->gate_up, S, 2 * I, H / 2, banks->slot_stride[0], SUPER * BK / 2, true))) return rc;
+    if ((rc = encode_bank_map(&g1.s_map, banks->gate_up_scale, S, 2 * I, H / 16, banks->slot_stride[1], SUPER * BK / 16, false))) return rc;
+  }
+  g1.w_staged = staged1;
   g1.packed = banks->gate_up;
   g1.scales = banks->gate_up_scale;
   g1.globals = banks->gate_up_global;
@@ -1079,26 +1097,27 @@ static int prefill_stages_impl(const void* x, const b200moe_banks* banks, const 
   g1.global_stride = banks->slot_stride[2];
   g1.N = 2 * I;
   g1.K = H;
-  g1.NT = I / 64;
+  g1.NT = I / (ITEM_N / 2);
+  g1.half_n = I;
   g1.mtiles = ws.mtiles;
   g1.num_mtiles = ws.num_mtiles;
   g1.sorted_routes = ws.sorted_routes;
   g1.topk_w = topk_weights;
-  g1.top_k = top_k;
-  g1.mode = 0;
+  g1.a_inv = ws.a_inv;
   g1.out = ws.ic2;
   g1.status = status;
-  const bool pair = pairs > 0 && g1.NT % 2 == 0 && (H / WM) % 2 == 0;
   if (stage_mask & B200MOE_STAGE_GEMM1) {
-    if (pair) rc = launch_grouped_gemm<0, true>(g1, (int)std::min<int64_t>(pairs, (int64_t)max_mtiles * (g1.NT / 2)), st);
-    else rc = launch_grouped_gemm<0, false>(g1, (int)std::min<int64_t>(sm_count, (int64_t)max_mtiles * g1.NT), st);
+    rc = launch_grouped_gemm<0>(g1, (int)std::min<int64_t>(pairs, (int64_t)max_mtiles * g1.NT), st);
     if (rc) return rc;
   }
 
   GgParams g2 = g1;
-  g2.a = ws.ic2;
-  g2.lda = I;
   if ((rc = encode_rows_map(&g2.a_map, ws.ic2, (int64_t)R + TN, I, I))) return rc;
+  if (staged2) {
+    if ((rc = encode_bank_map(&g2.w_map, banks->down, S, H, I / 2, banks->slot_stride[3], SUPER * BK / 2, true))) return rc;
+    if ((rc = encode_bank_map(&g2.s_map, banks->down_scale, S, H, I / 16, banks->slot_stride[4], SUPER * BK / 16, false))) return rc;
+  }
+  g2.w_staged = staged2;
   g2.packed = banks->down;
   g2.scales = banks->down_scale;
   g2.globals = banks->down_global;
@@ -1107,16 +1126,15 @@ static int prefill_stages_impl(const void* x, const b200moe_banks* banks, const 
   g2.global_stride = banks->slot_stride[5];
   g2.N = H;
   g2.K = I;
-  g2.NT = H / WM;
-  g2.mode = 1;
+  g2.NT = H / ITEM_N;
+  g2.a_inv = nullptr;
   g2.out = ws.ic3;
   g2.out_peers = reinterpret_cast<__nv_bfloat16* const*>(out_peers);
   g2.routes_per_rank = routes_per_rank > 0 ? routes_per_rank : 1;
   g2.route_offset = route_offset;
   g2.total_routes = total_routes > 0 ? total_routes : (int64_t)1 << 62;
   if (stage_mask & B200MOE_STAGE_GEMM2) {
-    if (pair) rc = launch_grouped_gemm<1, true>(g2, (int)std::min<int64_t>(pairs, (int64_t)max_mtiles * (g2.NT / 2)), st);
-    else rc = launch_grouped_gemm<1, false>(g2, (int)std::min<int64_t>(sm_count, (int64_t)max_mtiles * g2.NT), st);
+    rc = launch_grouped_gemm<1>(g2, (int)std::min<int64_t>(pairs, (int64_t)max_mtiles * g2.NT), st);
     if (rc) return rc;
   }
   if (stage_mask & B200MOE_STAGE_COMBINE) {
