@@ -54,9 +54,10 @@ constexpr int UNPACK_WARPS = 16, GROUPS = 4, GROUP_WARPS = UNPACK_WARPS / GROUPS
 constexpr int SUPER = GROUPS;                        // k-steps per staged weight block: 128 packed bytes of every row
 constexpr int W_PACKED_BYTES = WROWS * (SUPER * BK / 2), W_SCALE_BYTES = WROWS * (SUPER * BK / 16);
 constexpr int W_BYTES = W_PACKED_BYTES + W_SCALE_BYTES;
-// Ring depths.  Tokens: six k-steps; unpacked weights: four (one per unpack group); staged packed weights: three
-// blocks of four k-steps.
-constexpr int SA = 6, SB = 4, SW = 3;
+// Ring depths.  One slot per k-step holds the token rows and the unpacked weight rows (one tcgen05.commit frees
+// both): five k-steps; staged packed weights: three blocks of four k-steps.
+constexpr int ST = 5, SW = 3;
+constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
 constexpr int TMEM_COLS = 512;
 static_assert(GROUP_WARPS * 32 == WROWS, "one unpack thread per weight row of a k-step");
 static_assert(W_PACKED_BYTES % 1024 == 0 && W_BYTES % 1024 == 0, "swizzled tiles start on 1024-byte boundaries");
@@ -182,6 +183,22 @@ B200MOE_DEVICE void tc_mma_f16_pair(uint32_t d_tmem, uint64_t adesc, uint64_t bd
                ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
                : "memory");
 }
+// (a0, a1) * (b0, b1) in one instruction (packed fp32 multiply, round to nearest: the same results as two fmul)
+B200MOE_DEVICE float2 mul2(float a0, float a1, float b0, float b1) {
+  unsigned long long a, b, r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(a) : "f"(a0), "f"(a1));
+  asm("mov.b64 %0, {%1, %2};" : "=l"(b) : "f"(b0), "f"(b1));
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  float2 o;
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(o.x), "=f"(o.y) : "l"(r));
+  return o;
+}
+// true in exactly one lane of the (converged) warp
+B200MOE_DEVICE bool elect_one() {
+  uint32_t pred;
+  asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(pred));
+  return pred != 0;
+}
 B200MOE_DEVICE void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 // K-major operand tile, 128-byte rows, 128B swizzle, 8-row groups 1024 B apart (tile base 1024-aligned).
@@ -259,18 +276,33 @@ B200MOE_DEVICE void quad_transpose(uint32_t (&b)[4][NR], int j) {
 }
 
 struct alignas(16) GgShared {
-  unsigned long long full_a[SA], empty_a[SA], full_b[SB], empty_b[SB], part[SB], full_w[SW], empty_w[SW];
+  unsigned long long full[ST], empty[ST], part[ST], full_w[SW], empty_w[SW];
   unsigned long long tmem_full[2], tmem_empty[2], table[2];
   uint32_t tmem_base;
   int abort_flag;
   alignas(16) float gl[2][ITEM_N];  // per accumulator buffer: the fp32 global of every column of the item
 };
-constexpr size_t GG_SMEM = 1024 + (size_t)SA * A_BYTES + (size_t)SB * B_BYTES + (size_t)SW * W_BYTES + sizeof(GgShared);
+constexpr size_t GG_SMEM = 1024 + (size_t)ST * STAGE_BYTES + (size_t)SW * W_BYTES + sizeof(GgShared);
 
 // kind::f16 instruction descriptor: D fp32, A and B fp16, both K-major, M = m (over the pair), N = n.
 B200MOE_DEVICE uint32_t umma_idesc_f16(int n, int m) {
   return (1u << 4) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
 }
+
+// Cycle accounting of the roles of CTA 0 (diagnostic build, -DB200MOE_GG_PROFILE): every role adds up the cycles
+// it spends in its waits and in its work; read back with b200moe_debug_gg_profile.
+#ifdef B200MOE_GG_PROFILE
+__device__ long long g_gg_prof[2][32];
+#define PROF_DECL(n) long long prof[n] = {};
+#define PROF_T(var) const long long var = clock64();
+#define PROF_ADD(slot, a, b) prof[slot] += (b) - (a);
+#define PROF_OUT(base, n) if (blockIdx.x == 0) for (int i_ = 0; i_ < (n); ++i_) g_gg_prof[MODE][(base) + i_] = prof[i_];
+#else
+#define PROF_DECL(n)
+#define PROF_T(var)
+#define PROF_ADD(slot, a, b)
+#define PROF_OUT(base, n)
+#endif
 
 template <int MODE>
 __global__ void __launch_bounds__(Roles<MODE>::THREADS, 1) grouped_gemm_kernel(const __grid_constant__ GgParams p) {
@@ -278,21 +310,17 @@ __global__ void __launch_bounds__(Roles<MODE>::THREADS, 1) grouped_gemm_kernel(c
   constexpr int EPI_WARPS = R::EPI;
   extern __shared__ unsigned char smem_dyn[];
   unsigned char* ring = reinterpret_cast<unsigned char*>(((uintptr_t)smem_dyn + 1023) & ~(uintptr_t)1023);
-  GgShared* sh = reinterpret_cast<GgShared*>(ring + (size_t)SA * A_BYTES + (size_t)SB * B_BYTES + (size_t)SW * W_BYTES);
+  GgShared* sh = reinterpret_cast<GgShared*>(ring + (size_t)ST * STAGE_BYTES + (size_t)SW * W_BYTES);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const uint32_t ring_a = smem_u32(ring), ring_b = ring_a + SA * A_BYTES, ring_w = ring_b + SB * B_BYTES;
+  const uint32_t ring_u32 = smem_u32(ring), ring_w = ring_u32 + ST * STAGE_BYTES;
   volatile int* abort_flag = &sh->abort_flag;
   const int rank = (int)cluster_ctarank();
   const int unit = (int)(blockIdx.x >> 1), units = (int)(gridDim.x >> 1);
 
   if (tid == 0) {
-    for (int s = 0; s < SA; ++s) {
-      mbar_init(smem_u32(&sh->full_a[s]), 1);            // the leader's byte-count arrive (+ the bytes of both CTAs)
-      mbar_init(smem_u32(&sh->empty_a[s]), 1);           // the MMA thread's commit
-    }
-    for (int s = 0; s < SB; ++s) {
-      mbar_init(smem_u32(&sh->full_b[s]), 2);            // one relay per CTA
-      mbar_init(smem_u32(&sh->empty_b[s]), 1);           // the MMA thread's commit
+    for (int s = 0; s < ST; ++s) {
+      mbar_init(smem_u32(&sh->full[s]), 3);              // the leader's byte-count arrive (+ the bytes of both CTAs), one relay per CTA
+      mbar_init(smem_u32(&sh->empty[s]), 1);             // the MMA thread's commit
       mbar_init(smem_u32(&sh->part[s]), GROUP_WARPS);    // this CTA's unpack warps of the k-step's group
     }
     for (int s = 0; s < SW; ++s) {
@@ -338,6 +366,7 @@ __global__ void __launch_bounds__(Roles<MODE>::THREADS, 1) grouped_gemm_kernel(c
     constexpr int CH = EPI_WARPS / 4;
     constexpr int NR = MODE == 0 ? 4 : 8;   // registers of one 16-column chunk after conversion (8 fp16 / 16 bf16)
     int tl = 0;
+    PROF_DECL(3)
     for (int item = unit; item < total_items; item += units, ++tl) {
       const int tt = item / NT, wt = item - tt * NT;
       const int4 info = p.mtiles[tt];
@@ -376,13 +405,10 @@ __global__ void __launch_bounds__(Roles<MODE>::THREADS, 1) grouped_gemm_kernel(c
         dst = reinterpret_cast<char*>(base + wt * ITEM_N + n_base);
       }
       if (!valid) dst = nullptr;
-      // destinations of the four tokens of this lane's quad
-      char* dstq[4];
-#pragma unroll
-      for (int k = 0; k < 4; ++k)
-        dstq[k] = reinterpret_cast<char*>(__shfl_sync(0xffffffffu, (unsigned long long)(uintptr_t)dst, (lane & ~3) + k));
+      PROF_T(e0)
       const bool ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&sh->tmem_full[buf]), (tl >> 1) & 1, abort_flag));
       if (!ok) break;
+      PROF_T(e1)
       tc_fence_after();
       const uint32_t tbase = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * ITEM_N + col0);
       const float* glt = &sh->gl[buf][n_base];
@@ -395,12 +421,12 @@ __global__ void __launch_bounds__(Roles<MODE>::THREADS, 1) grouped_gemm_kernel(c
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
             const float4 g = g4[i];  // gate, up, gate, up
-            const float gate0 = bf16_round((__uint_as_float(v[4 * i]) * mul) * g.x);
-            const float up0 = bf16_round((__uint_as_float(v[4 * i + 1]) * mul) * g.y);
-            const float gate1 = bf16_round((__uint_as_float(v[4 * i + 2]) * mul) * g.z);
-            const float up1 = bf16_round((__uint_as_float(v[4 * i + 3]) * mul) * g.w);
-            y[2 * i] = bf16_round(silu_mul(gate0, up0));
-            y[2 * i + 1] = bf16_round(silu_mul(gate1, up1));
+            float2 a = mul2(__uint_as_float(v[4 * i]), __uint_as_float(v[4 * i + 1]), mul, mul);
+            float2 b = mul2(__uint_as_float(v[4 * i + 2]), __uint_as_float(v[4 * i + 3]), mul, mul);
+            a = mul2(a.x, a.y, g.x, g.y);
+            b = mul2(b.x, b.y, g.z, g.w);
+            y[2 * i] = bf16_round(silu_mul(bf16_round(a.x), bf16_round(a.y)));
+            y[2 * i + 1] = bf16_round(silu_mul(bf16_round(b.x), bf16_round(b.y)));
           }
 #pragma unroll
           for (int i = 0; i < 4; ++i) o[i] = pack_f16x2_sat(y[2 * i], y[2 * i + 1]);
@@ -408,8 +434,12 @@ __global__ void __launch_bounds__(Roles<MODE>::THREADS, 1) grouped_gemm_kernel(c
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
             const float4 g = g4[i];
-            o[2 * i] = pack_bf16x2((__uint_as_float(v[4 * i]) * g.x) * mul, (__uint_as_float(v[4 * i + 1]) * g.y) * mul);
-            o[2 * i + 1] = pack_bf16x2((__uint_as_float(v[4 * i + 2]) * g.z) * mul, (__uint_as_float(v[4 * i + 3]) * g.w) * mul);
+            float2 a = mul2(__uint_as_float(v[4 * i]), __uint_as_float(v[4 * i + 1]), g.x, g.y);
+            float2 b = mul2(__uint_as_float(v[4 * i + 2]), __uint_as_float(v[4 * i + 3]), g.z, g.w);
+            a = mul2(a.x, a.y, mul, mul);
+            b = mul2(b.x, b.y, mul, mul);
+            o[2 * i] = pack_bf16x2(a.x, a.y);
+            o[2 * i + 1] = pack_bf16x2(b.x, b.y);
           }
         }
       };
@@ -430,8 +460,10 @@ __global__ void __launch_bounds__(Roles<MODE>::THREADS, 1) grouped_gemm_kernel(c
         const int gbyte = MODE == 0 ? c : 2 * c;
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
-          if (dstq[k] == nullptr) continue;
-          char* d = dstq[k] + gbyte + jq * (NR * 4);
+          // destination of token k of this lane's quad
+          char* dk = reinterpret_cast<char*>(__shfl_sync(0xffffffffu, (unsigned long long)(uintptr_t)dst, (lane & ~3) + k));
+          if (dk == nullptr) continue;
+          char* d = dk + gbyte + jq * (NR * 4);
           stg_v4(d, make_uint4(blk[k][0], blk[k][1], blk[k][2], blk[k][3]));
           if (NR == 8) stg_v4(d + 16, make_uint4(blk[k][NR - 4], blk[k][NR - 3], blk[k][NR - 2], blk[k][NR - 1]));
         }
@@ -439,7 +471,10 @@ __global__ void __launch_bounds__(Roles<MODE>::THREADS, 1) grouped_gemm_kernel(c
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(leader(&sh->tmem_empty[buf]));
+      PROF_T(e2)
+      PROF_ADD(0, e0, e1) PROF_ADD(1, e1, e2) PROF_ADD(2, 0, 1)
     }
+    if (tid == 0) { PROF_OUT(0, 3) }
   } else if (warp < R::TMA_A) {
     // ------------------------------------------------------------------ weight unpackers
     regs_give<R::REGS_UNPACK>();
@@ -447,29 +482,35 @@ __global__ void __launch_bounds__(Roles<MODE>::THREADS, 1) grouped_gemm_kernel(c
     const int u = warp - R::UNPACK0, grp = u / GROUP_WARPS, l = (u % GROUP_WARPS) * 32 + lane;
     const int j = rank * WROWS + l;  // row inside the item
     const uint32_t b_row = l * 128, b_x = l & 7;
-    // unpacked row -> the k-step's B slot, then tell the relay
-    auto store_row = [&](uint32_t it, const uint4 (&c)[8]) -> bool {
-      const int s = it % SB;
-      if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&sh->empty_b[s]), ((it / SB) & 1) ^ 1, abort_flag))) return false;
-      const uint32_t sb = ring_b + s * B_BYTES + b_row;
+    PROF_DECL(4)
+    // One row of a k-step: unpack, wait for the slot, store, fence, tell the relay.  gate_up unpacks into registers
+    // BEFORE it waits (the wait -> store -> fence -> relay chain is what the MMA thread waits for); down, with 28
+    // warps and 72 registers per thread, unpacks chunk by chunk after the wait.  `release` runs once the packed
+    // registers have been consumed (the staged path frees its block there).
+    auto produce_row = [&](uint32_t it, const uint4& q0, const uint4& q1, uint32_t sc, auto release) -> bool {
+      const int s = it % ST;
+      const uint32_t s01 = e4m3x2_to_f16x2(sc & 0xffffu), s23 = e4m3x2_to_f16x2(sc >> 16);
+      const uint32_t sc0 = dup_lo16(s01), sc1 = dup_hi16(s01), sc2 = dup_lo16(s23), sc3 = dup_hi16(s23);
+      const uint32_t w[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+      const uint32_t sw[4] = {sc0, sc1, sc2, sc3};
+      uint4 c[8];
+      if (MODE == 0) {
 #pragma unroll
-      for (int i = 0; i < 8; ++i) sts_v4(sb + ((i ^ b_x) << 4), c[i]);
+        for (int i = 0; i < 8; ++i) c[i] = unpack_chunk_f16(w[i], sw[i >> 1]);
+        release();
+      }
+      PROF_T(u0)
+      if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&sh->empty[s]), ((it / ST) & 1) ^ 1, abort_flag))) return false;
+      PROF_T(u1)
+      PROF_ADD(1, u0, u1)
+      const uint32_t sb = ring_u32 + s * STAGE_BYTES + A_BYTES + b_row;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) sts_v4(sb + ((i ^ b_x) << 4), MODE == 0 ? c[i] : unpack_chunk_f16(w[i], sw[i >> 1]));
+      if (MODE != 0) release();
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&sh->part[s]));
       return true;
-    };
-    auto unpack_row = [&](const uint4& q0, const uint4& q1, uint32_t sc, uint4 (&c)[8]) {
-      const uint32_t s01 = e4m3x2_to_f16x2(sc & 0xffffu), s23 = e4m3x2_to_f16x2(sc >> 16);
-      const uint32_t sc0 = dup_lo16(s01), sc1 = dup_hi16(s01), sc2 = dup_lo16(s23), sc3 = dup_hi16(s23);
-      c[0] = unpack_chunk_f16(q0.x, sc0);
-      c[1] = unpack_chunk_f16(q0.y, sc0);
-      c[2] = unpack_chunk_f16(q0.z, sc1);
-      c[3] = unpack_chunk_f16(q0.w, sc1);
-      c[4] = unpack_chunk_f16(q1.x, sc2);
-      c[5] = unpack_chunk_f16(q1.y, sc2);
-      c[6] = unpack_chunk_f16(q1.z, sc3);
-      c[7] = unpack_chunk_f16(q1.w, sc3);
     };
     if (p.w_staged) {
       // The packed bytes of four k-steps of every row sit in a staged block: rows in box order (gate_up: 64 gate
@@ -481,16 +522,22 @@ __global__ void __launch_bounds__(Roles<MODE>::THREADS, 1) grouped_gemm_kernel(c
       for (uint32_t it = grp; it < total_steps; it += GROUPS) {
         const uint32_t blk = it / SUPER;
         const int ws = blk % SW;
+        PROF_T(w0)
         if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&sh->full_w[ws]), (blk / SW) & 1, abort_flag))) break;
+        PROF_T(w1)
+        PROF_ADD(0, w0, w1) PROF_ADD(3, 0, 1)
         const uint32_t wb = ring_w + ws * W_BYTES;
         const uint4 q0 = lds_v4(wb + w_off0), q1 = lds_v4(wb + w_off1);
         const uint32_t sc = lds_u32(wb + s_off);
-        uint4 c[8];
-        unpack_row(q0, q1, sc, c);
-        __syncwarp();
-        if (lane == 0) mbar_arrive(smem_u32(&sh->empty_w[ws]));  // this warp holds its part of the block in registers
-        if (!store_row(it, c)) break;
+        const bool stored = produce_row(it, q0, q1, sc, [&]() {
+          __syncwarp();
+          if (lane == 0) mbar_arrive(smem_u32(&sh->empty_w[ws]));  // every lane has consumed its part of the block
+        });
+        if (!stored) break;
+        PROF_T(w2)
+        PROF_ADD(2, w1, w2)
       }
+      if (tid == R::UNPACK0 * 32) { PROF_OUT(4, 4) }
     } else {
       // Reductions that are not a multiple of 256 (small test shapes): every thread reads its row from global memory,
       // three of its steps ahead.  The loop is unrolled over the three register sets, so a set is only read again
@@ -524,9 +571,7 @@ __global__ void __launch_bounds__(Roles<MODE>::THREADS, 1) grouped_gemm_kernel(c
         }
       };
       auto step = [&](WRegs& r, uint32_t it) -> bool {
-        uint4 c[8];
-        unpack_row(r.q0, r.q1, r.sc, c);
-        if (!store_row(it, c)) return false;
+        if (!produce_row(it, r.q0, r.q1, r.sc, []() {})) return false;
         fetch(r);
         return true;
       };
@@ -555,12 +600,12 @@ __global__ void __launch_bounds__(Roles<MODE>::THREADS, 1) grouped_gemm_kernel(c
         const int row0 = info.y + rank * (half ? 64 : TOK_ROWS);
         const int boxes = half ? 1 : 2;
         for (int kb = 0; kb < KB; ++kb, ++it) {
-          const int s = it % SA;
-          ok = mbar_wait(smem_u32(&sh->empty_a[s]), ((it / SA) & 1) ^ 1, abort_flag);
+          const int s = it % ST;
+          ok = mbar_wait(smem_u32(&sh->empty[s]), ((it / ST) & 1) ^ 1, abort_flag);
           if (!ok) break;
-          const uint32_t sa = ring_a + s * A_BYTES;
-          const uint32_t bar = leader(&sh->full_a[s]);
-          if (rank == 0) mbar_arrive_expect_tx(smem_u32(&sh->full_a[s]), 2u * (uint32_t)boxes * (64u * 128u));
+          const uint32_t sa = ring_u32 + s * STAGE_BYTES;
+          const uint32_t bar = leader(&sh->full[s]);
+          if (rank == 0) mbar_arrive_expect_tx(smem_u32(&sh->full[s]), 2u * (uint32_t)boxes * (64u * 128u));
           for (int b = 0; b < boxes; ++b) tma_load_2d_pair(sa + b * (64 * 128), &p.a_map, kb * BK, row0 + b * 64, bar);
         }
       }
@@ -601,63 +646,75 @@ __global__ void __launch_bounds__(Roles<MODE>::THREADS, 1) grouped_gemm_kernel(c
     // ------------------------------------------------------------------ relay: this CTA's weight half of a k-step -> leader
     // (no proxy fence here: the unpackers fenced their own stores)
     if (lane == 0) {
-      const uint32_t leader_full = leader(&sh->full_b[0]);
+      const uint32_t leader_full = leader(&sh->full[0]);
       for (uint32_t it = 0; it < total_steps; ++it) {
-        const int s = it % SB;
-        if (!mbar_wait(smem_u32(&sh->part[s]), (it / SB) & 1, abort_flag)) break;
+        const int s = it % ST;
+        if (!mbar_wait(smem_u32(&sh->part[s]), (it / ST) & 1, abort_flag)) break;
         mbar_arrive_cluster(leader_full + s * 8);
       }
     }
   } else {
     // ------------------------------------------------------------------ MMA issuer (the pair's leader only)
-    if (lane == 0 && rank == 0) {
+    // The whole warp walks the loop and waits on the barriers, one elected lane issues: loop state that is the same
+    // in every lane stays in uniform registers, which the tcgen05 instructions take their operands from (a loop
+    // inside "if (lane == 0)" pays a register-to-uniform move per operand per instruction).
+    if (rank == 0) {
       int tl = 0;
       bool ok = true;
-      int sa = 0, sb = 0;
-      uint32_t phase_a = 0, phase_b = 0;
-      const uint32_t full_a0 = smem_u32(&sh->full_a[0]), empty_a0 = smem_u32(&sh->empty_a[0]);
-      const uint32_t full_b0 = smem_u32(&sh->full_b[0]), empty_b0 = smem_u32(&sh->empty_b[0]);
-      const uint64_t ad0 = umma_desc_sw128(ring_a), bd0 = umma_desc_sw128(ring_b);
-      constexpr uint64_t SLOT_UNITS = A_BYTES >> 4;  // descriptor start addresses count 16-byte units
+      int s = 0;
+      uint32_t phase = 0;
+      const uint32_t full0 = smem_u32(&sh->full[0]), empty0 = smem_u32(&sh->empty[0]);
+      const uint64_t ad0 = umma_desc_sw128(ring_u32), bd0 = umma_desc_sw128(ring_u32 + A_BYTES);
+      constexpr uint64_t STAGE_UNITS = STAGE_BYTES >> 4;  // descriptor start addresses count 16-byte units
       uint64_t ad = ad0, bd = bd0;
       int half_next = unit < total_items ? p.mtiles[unit / NT].w : 0;
+      PROF_DECL(7)
+      PROF_T(m_start)
       for (int item = unit; item < total_items && ok; item += units, ++tl) {
         const int half = half_next;
         if (item + units < total_items) half_next = p.mtiles[(item + units) / NT].w;  // needed one item from now
         const uint32_t idesc = umma_idesc_f16(ITEM_N, half ? TOK_ROWS : 2 * TOK_ROWS);
         const int buf = tl & 1;
+        PROF_T(m0)
         if (!mbar_wait(smem_u32(&sh->tmem_empty[buf]), ((tl >> 1) & 1) ^ 1, abort_flag)) break;
+        PROF_T(m1)
+        PROF_ADD(4, m0, m1)
         tc_fence_after();
         const uint32_t d = tmem_base + (uint32_t)(buf * ITEM_N);
         for (int kb = 0; kb < KB; ++kb) {
-          if (!mbar_wait(full_b0 + 8 * sb, phase_b, abort_flag) || !mbar_wait(full_a0 + 8 * sa, phase_a, abort_flag)) {
+          PROF_T(k0)
+          if (!mbar_wait(full0 + 8 * s, phase, abort_flag)) {
             ok = false;
             break;
           }
+          PROF_T(k2)
           tc_fence_after();
-          tc_mma_f16_pair(d, ad, bd, idesc, kb != 0);
-          tc_mma_f16_pair(d, ad + 2, bd + 2, idesc, 1);
-          tc_mma_f16_pair(d, ad + 4, bd + 4, idesc, 1);
-          tc_mma_f16_pair(d, ad + 6, bd + 6, idesc, 1);
-          tc_commit_pair(empty_a0 + 8 * sa, 3);
-          tc_commit_pair(empty_b0 + 8 * sb, 3);
-          if (++sa == SA) {
-            sa = 0;
-            phase_a ^= 1;
-            ad = ad0;
-          } else {
-            ad += SLOT_UNITS;
+          if (elect_one()) {
+            tc_mma_f16_pair(d, ad, bd, idesc, kb != 0);
+            tc_mma_f16_pair(d, ad + 2, bd + 2, idesc, 1);
+            tc_mma_f16_pair(d, ad + 4, bd + 4, idesc, 1);
+            tc_mma_f16_pair(d, ad + 6, bd + 6, idesc, 1);
+            tc_commit_pair(empty0 + 8 * s, 3);
           }
-          if (++sb == SB) {
-            sb = 0;
-            phase_b ^= 1;
+          __syncwarp();
+          PROF_T(k4)
+          PROF_ADD(0, k0, k2) PROF_ADD(2, k2, k4) PROF_ADD(5, 0, 1)
+          if (++s == ST) {
+            s = 0;
+            phase ^= 1;
+            ad = ad0;
             bd = bd0;
           } else {
-            bd += SLOT_UNITS;
+            ad += STAGE_UNITS;
+            bd += STAGE_UNITS;
           }
         }
-        if (ok) tc_commit_pair(smem_u32(&sh->tmem_full[buf]), 3);
+        if (ok && elect_one()) tc_commit_pair(smem_u32(&sh->tmem_full[buf]), 3);
+        __syncwarp();
       }
+      PROF_T(m_end)
+      PROF_ADD(6, m_start, m_end)
+      if (lane == 0) { PROF_OUT(8, 7) }
     }
     __syncwarp();
    }
@@ -954,6 +1011,12 @@ static int encode_bank_map(CUtensorMap* map, const void* base, int64_t slots, in
 }  // namespace b200moe
 
 using namespace b200moe;
+
+#ifdef B200MOE_GG_PROFILE
+extern "C" int b200moe_debug_gg_profile(long long* host_out) {
+  return (int)cudaMemcpyFromSymbol(host_out, g_gg_prof, sizeof(long long) * 2 * 32);
+}
+#endif
 
 extern "C" int64_t b200moe_prefill_workspace_bytes(int T, int top_k, int hidden, int intermediate, int num_slots) {
   if (T < 0 || top_k < 1 || num_slots < 1) return 0;
