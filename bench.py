@@ -4,8 +4,9 @@
 
 One "step" = one pass of the whole MoE block (router, permutation, expert GEMMs with SwiGLU, shared expert,
 weighted combine + merge) over one batch of synthetic tokens.  N=1 runs the prefill workload the headline
-metric is quoted on (T=8192, Zipf(1.1) routing over 256 experts); N>1 runs expert-parallel prefill with
-8192 tokens per GPU (T=65536 at N=8).  Prints ONE JSON line on rank 0.
+metric is quoted on (T=8192, Zipf(1.1) routing over 256 experts) plus the T=1024/32768/65536 points, the decode
+layer and the slot-cache workload; N>1 runs expert-parallel prefill of T=65536 tokens split evenly over the
+ranks, experts in contiguous blocks.  Prints ONE JSON line on rank 0.
 """
 from __future__ import annotations
 
@@ -25,10 +26,12 @@ sys.path.insert(0, str(ROOT))
 METRIC = "moe_prefill_tokens_per_s"
 UNIT = "tokens/s"
 TOKENS_PER_GPU = 8192
+EP_TOTAL_TOKENS = 65536
 NVFP4_DENSE_PEAK_TFLOPS = 9000.0  # nominal dense NVFP4 tensor peak of one B200
-# dram__bytes_read.sum + dram__bytes_write.sum of one gate_up grouped-GEMM launch at T=8192, from the ncu capture
-# summarised in profiles/grouped_gemm_ws_prefill_T8192.md (518.5 MB + 52.7 MB)
-NCU_TRAFFIC_GEMM1_T8192_BYTES = 571_166_720
+# DRAM traffic of one gate_up grouped-GEMM launch at T=8192 (dram__bytes_read.sum + dram__bytes_write.sum of a
+# one-kernel ncu capture of this command with --steps 1); the JSON line names the capture it came from.
+NCU_TRAFFIC_GEMM1_T8192 = {"bytes": None, "read": None, "write": None, "capture": None}
+CPU_TOKENS = 8192  # the CPU arms run the same T as the headline
 
 
 def load_peaks() -> dict:
@@ -92,8 +95,9 @@ class ClockSampler:
                 "samples": len(self.rows)}
 
 
-def cpu_baseline(tokens: int, threads: int) -> dict:
-    """The oracle (a port of the reference's torch dequantise-and-matmul path) on this box's host cores."""
+def cpu_baseline(tokens: int, threads: int, warmup: int = 1, reps: int = 3) -> dict:
+    """The oracle (a port of the reference's torch dequantise-and-matmul path) on this box's host cores, on the
+    SAME workload as the GPU arm: whole block, T tokens, seeded Zipf(1.1) routing."""
     import torch
 
     import oracle
@@ -101,15 +105,16 @@ def cpu_baseline(tokens: int, threads: int) -> dict:
 
     torch.set_num_threads(threads)
     layer = synth.make_layer(0, tokens, zipf_alpha=1.1)
-    oracle.moe_block(layer, 8)  # warm-up
+    for _ in range(warmup):
+        oracle.moe_block(layer, 8)
     times = []
-    for _ in range(2):
+    for _ in range(reps):
         t0 = time.perf_counter()
         oracle.moe_block(layer, 8)
         times.append(time.perf_counter() - t0)
-    return {"value": tokens / min(times), "unit": UNIT, "cores": threads, "kind": "port",
-            "sample": f"whole MoE block, T={tokens} of the same seeded Zipf(1.1) workload, best of 2 after 1 warm-up, "
-                      f"torch {torch.__version__} fp32 on {threads} threads"}
+    return {"value": tokens / statistics.median(times), "unit": UNIT, "cores": threads, "kind": "port",
+            "sample": f"whole MoE block, T={tokens} (the headline workload: same seed, same Zipf(1.1) routing), median of "
+                      f"{reps} after {warmup} warm-up, torch {torch.__version__} fp32 on {threads} threads"}
 
 
 def run_reference(args) -> None:
@@ -123,7 +128,7 @@ def run_reference(args) -> None:
     from qwen36_moe_16gb_b200 import synth
 
     torch.set_num_threads(threads)
-    tokens = 256  # bounded sample of the T=8192 workload: every step touches (nearly) all 256 experts
+    tokens = CPU_TOKENS  # the same workload as the GPU arm (one step is a few seconds of CPU work)
     layer = synth.make_layer(0, tokens, zipf_alpha=1.1)
     for _ in range(args.warmup):
         oracle.moe_block(layer, 8)
@@ -133,11 +138,11 @@ def run_reference(args) -> None:
     dt = (time.perf_counter() - t0) / args.steps
     val = tokens / dt
     cb = {"value": val, "unit": UNIT, "cores": threads, "kind": "port",
-          "sample": f"T={tokens} tokens per step of the seeded Zipf(1.1) prefill workload (CPU oracle, fp32 torch)"}
+          "sample": f"T={tokens} tokens per step: the whole seeded Zipf(1.1) prefill workload (CPU oracle, fp32 torch)"}
     print(json.dumps({"impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus,
                       "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
                       "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-                      "config": {"workload": f"prefill_T{TOKENS_PER_GPU}_zipf1.1", "sample_tokens": tokens},
+                      "config": {"workload": f"prefill_T{TOKENS_PER_GPU}_zipf1.1", "tokens_per_step": tokens},
                       "cpu_baseline": cb,
                       "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}))
 
@@ -238,11 +243,107 @@ def cache_bench(torch, steps: int = 512, layers: int = 40, slots: int = 4603) ->
     stack.cache.reset_stats()
     res = stack.run(routing)
     out = {k: (round(v, 4) if isinstance(v, float) else v) for k, v in res.items() if k != "out"}
+    out["policy_bit_exact"] = cache_policy_check(stack, routing, warm=8)
     out.update(layers=layers, slots=slots, host_bank_gb=round(layers * 256 * synth.QWEN36.expert_bytes / 1e9, 3),
                setup_s=round(setup_s, 1), routing="Zipf(1.1), 70% reuse, seed 0", plan="host LRU + cudaMemcpyAsync on a copy stream")
     del stack
     torch.cuda.empty_cache()
     return out
+
+
+def cache_policy_check(stack, routing, warm: int) -> dict:
+    """NOT timed: replays the same routing (warm-up steps, then the measured steps) through the CPU policy oracle
+    and compares the ordered miss plan of every (step, layer) of the measured run and the final slot tables."""
+    import numpy as np
+
+    import oracle
+
+    cache = stack.cache
+    o = oracle.SlotCacheOracle(cache.num_layers, cache.num_experts, cache.cache_size)
+    for s_ in range(warm):
+        for layer in range(cache.num_layers):
+            o.ensure(layer, routing[s_, layer].numpy())
+    plans_equal, c = True, 0
+    for s_ in range(routing.shape[0]):
+        for layer in range(cache.num_layers):
+            o.ensure(layer, routing[s_, layer].numpy())
+            src, dst = stack.miss_log[c]
+            plans_equal &= src == o.src_indices.tolist() and dst == o.evict_slots.tolist()
+            c += 1
+    tables_equal = (np.array_equal(cache.slot_for_id.view(-1).numpy(), o.slot_for_id)
+                    and np.array_equal(cache.id_of_slot.numpy(), o.id_of_slot)
+                    and np.array_equal(cache.usage.numpy(), o.usage) and int(cache.step) == o.step)
+    return {"miss_plans": bool(plans_equal), "tables": bool(tables_equal), "calls_compared": c,
+            "checker": "oracle.SlotCacheOracle replay, outside the timed region"}
+
+
+def prefill_point(torch, ops, synth, blk, banks, tokens: int, peaks: dict, steps: int, seed: int) -> dict:
+    """One more point of the prefill curve on the layer that is already on the device: `tokens` fresh tokens
+    (seeded), whole-block time and the time of every stage of the expert path."""
+    shape = synth.QWEN36
+    dev = blk.router_w.device
+    g = torch.Generator(device=dev).manual_seed(seed)
+    x = torch.randn(tokens, shape.hidden, generator=g, device=dev).to(torch.bfloat16)
+    out = torch.empty_like(x)
+
+    def step():
+        logits = blk.router_logits(x)
+        shared, gate = blk.shared_parts(x)
+        w, ids = ops.fused_topk(x, logits, shape.top_k, True)
+        ops.prefill_experts(x, banks, w, ids, shared=shared, shared_gate_logit=gate, out=out)
+
+    for _ in range(3):
+        step()
+    ms = time_events(step, steps, torch)
+    logits = blk.router_logits(x)
+    shared, gate = blk.shared_parts(x)
+    w, ids = ops.fused_topk(x, logits, shape.top_k, True)
+    ops.prefill_experts(x, banks, w, ids, shared=shared, shared_gate_logit=gate, out=out, check_status=True)
+    stage = {}
+    for name, mask in (("plan", ops.STAGE_PLAN), ("gemm1_gate_up_swiglu", ops.STAGE_GEMM1), ("gemm2_down", ops.STAGE_GEMM2),
+                       ("combine_merge", ops.STAGE_COMBINE)):
+        stage[name] = time_events(lambda: ops.prefill_experts(x, banks, w, ids, shared=shared, shared_gate_logit=gate,
+                                                              out=out, stages=mask), steps, torch)
+    distinct = int(torch.unique(ids).numel())
+    flops = synth.routed_flops(tokens, shape)
+    gemm_ms = stage["gemm1_gate_up_swiglu"] + stage["gemm2_down"]
+    tf = flops / (gemm_ms * 1e-3) / 1e12
+    gbs = synth.algorithmic_bytes(tokens, distinct, shape) / (ms * 1e-3) / 1e9
+    res = {"tokens": tokens, "ms_per_step": round(ms, 4), "tokens_per_s": round(tokens / (ms * 1e-3), 1),
+           "stages_ms": {k: round(v, 4) for k, v in stage.items()}, "routed_tflops": round(tf, 1),
+           "frac_of_measured_bf16_peak": round(tf / peaks["bf16_tflops"], 4),
+           "frac_of_nominal_nvfp4_peak": round(tf / NVFP4_DENSE_PEAK_TFLOPS, 4),
+           "distinct_experts": distinct, "hbm_gbs_algorithmic": round(gbs, 1),
+           "frac_of_measured_hbm": round(gbs / peaks["hbm_gbs"], 4)}
+    del x, out
+    torch.cuda.empty_cache()
+    return res
+
+
+def ep_checks(torch, dist, runner, rank: int, sample: int = 16) -> dict:
+    """NOT timed.  (1) no rank's kernels gave up on a bounded wait; (2) rank 0's output rows of `sample` of its
+    tokens against the CPU oracle fed the same routing and the banks collected from their owners."""
+    out = runner.step().clone()
+    torch.cuda.synchronize()
+    status_ok = runner.status_ok()
+    w, ids = runner.last_routing
+    banks = runner.gather_banks_to_host()   # collective: every rank takes part
+    res = {"status_ok": status_ok}
+    if rank == 0:
+        import oracle
+
+        t = runner.x.shape[0]
+        pick = torch.linspace(0, t - 1, sample).long()
+        x = runner.x[pick.to(runner.x.device)].cpu()
+        blk = runner.block
+        layer = dict(banks)
+        routed = oracle.moe_experts_bf16(x, layer, w[pick.to(w.device)].cpu(), ids[pick.to(ids.device)].cpu())
+        shared, gate = oracle.shared_expert(x, blk.shared_gate_up.cpu(), blk.shared_down.cpu(), blk.shared_gate.cpu())
+        want = oracle.shared_epilogue(routed, shared, gate)
+        max_abs, rel_l2 = oracle.error_metrics(out[pick.to(out.device)].float().cpu(), want.float())
+        res["parity"] = {"tokens": sample, "max_abs": max_abs, "rel_l2": rel_l2, "ok": bool(max_abs <= 2e-2 and rel_l2 <= 1e-3),
+                         "gate": "max-abs 2e-2, rel-L2 1e-3 against oracle.moe_experts_bf16 + shared expert"}
+    return res
 
 
 def run_ours(args) -> None:
@@ -267,7 +368,8 @@ def run_ours(args) -> None:
 
     peaks = load_peaks()
     shape = synth.QWEN36
-    T = TOKENS_PER_GPU
+    # one GPU: the headline workload (T=8192); expert parallel: the stated T=65536 split evenly over the ranks
+    T = TOKENS_PER_GPU if world == 1 else EP_TOTAL_TOKENS // world
     dev = torch.device("cuda", local)
     if args.only_decode:
         ms_ = tuple(int(v) for v in args.decode_m.split(","))
@@ -277,7 +379,7 @@ def run_ours(args) -> None:
     if world > 1:
         from qwen36_moe_16gb_b200 import ep
 
-        runner = ep.EpPrefill.synthetic(dist, shape, T, seed=0)
+        runner = ep.EpPrefill.synthetic(dist, shape, T, seed=0, placement="contiguous")
         step, pipe, info = runner.step, runner.pipeline(), runner.info
         launches_per_step = runner.launches_per_step
         stage_ms = None
@@ -309,7 +411,9 @@ def run_ours(args) -> None:
         pipe = HostPipeline(run_block, x_host, out_host, dev)
 
         info = {"h2d": x_host.numel() * 2, "d2h": out_host.numel() * 2}
-        launches_per_step = 10  # router, 4 permutation, tile list, 2 grouped GEMMs, combine, silu_and_mul
+        # this package's kernels per step: router top-k, 4 permutation, tile list, token gather, 2 grouped GEMMs,
+        # combine, silu_and_mul (the four dense GEMMs of router and shared expert are cuBLAS and not counted)
+        launches_per_step = 11
 
     for _ in range(max(args.warmup, 3)):
         step()
@@ -336,17 +440,40 @@ def run_ours(args) -> None:
         e2e_ms = float(t)
 
     total_tokens = T * world
+    ep_extra = {}
+    if world > 1:
+        ep_extra = ep_checks(torch, dist, runner, rank)
+        if not args.no_balanced:
+            # the same step with the experts dealt by route count instead of contiguous blocks (a deployment
+            # choice, reported beside the stated workload)
+            del pipe
+            balanced = ep.EpPrefill.synthetic(dist, shape, T, seed=0, placement="balanced")
+            for _ in range(3):
+                balanced.step()
+            torch.cuda.synchronize()
+            dist.barrier()
+            bms = torch.tensor([time_events(balanced.step, args.steps, torch)], device=dev)
+            dist.all_reduce(bms, op=dist.ReduceOp.MAX)
+            ep_extra["value_balanced"] = total_tokens / (float(bms) * 1e-3)
+            ep_extra["status_ok_balanced"] = balanced.status_ok()
     result = {"metric": METRIC, "value": total_tokens / (ms * 1e-3), "unit": UNIT, "n_gpus": world, "steps": args.steps,
-              "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+              "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True,
+              "scaling": "weak" if world == 1 else "strong",
               "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
               "config": {"workload": f"prefill_T{T}_zipf1.1" if world == 1 else f"ep_prefill_T{total_tokens}_zipf1.1",
                          "tokens_per_gpu": T, "hidden": 2048, "moe_intermediate": 512, "experts": 256, "top_k": 8,
-                         "weights": "NVFP4 (E2M1 + E4M3 per 16 + fp32 per row), bf16 activations, fp32 accumulate",
+                         "weights": "NVFP4 (E2M1 + E4M3 per 16 + fp32 per row), bf16 activations (fp16 inside the MMA, rows "
+                                    "rescaled by powers of two), fp32 accumulate",
                          "l2": "inputs larger than L2 (456 MB of expert weights per step)",
                          "parallelism": "single GPU" if world == 1 else f"ep{world}"},
               "e2e": {"value": total_tokens / (e2e_ms * 1e-3), "unit": UNIT, "h2d_bytes_per_step": info["h2d"],
                       "d2h_bytes_per_step": info["d2h"]},
               "gpu_launches": launches_per_step * args.steps, "clocks": clocks.summary()}
+    if world > 1:
+        result["config"]["expert_placement"] = "contiguous blocks of %d experts per GPU" % (shape.num_experts // world)
+        result["collective"] = ("symmetric-memory peer copies (token dispatch) + peer stores from the down GEMM's "
+                                "epilogue (combine); NCCL only for set-up, timing and the checks")
+        result.update(ep_extra)
 
     if world == 1:
         # per-stage device time of the expert path (same stream, events), for the roofline of the dominant kernel
@@ -363,17 +490,23 @@ def run_ours(args) -> None:
         flops1 = T * shape.top_k * 2 * shape.hidden * 2 * shape.intermediate
         flops2 = T * shape.top_k * 2 * shape.intermediate * shape.hidden
         ach = flops1 / (stage_ms["gemm1_gate_up_swiglu"] * 1e-3) / 1e12
-        result["roofline"] = {"bound": "tensor", "kernel": "grouped_gemm_ws_kernel<0> (gate_up + SwiGLU)", "achieved": ach,
+        result["roofline"] = {"bound": "tensor", "kernel": "grouped_gemm_kernel<0> (gate_up + SwiGLU)", "achieved": ach,
                               "peak": peaks["bf16_tflops"], "unit": "TFLOP/s", "frac": ach / peaks["bf16_tflops"],
                               "peak_source": f"{peaks['source']} cuBLAS bf16 burst (the kernel multiplies in kind::f16)",
                               "frac_of_nominal_nvfp4_peak": ach / NVFP4_DENSE_PEAK_TFLOPS,
-                              "traffic": NCU_TRAFFIC_GEMM1_T8192_BYTES, "traffic_unit": "bytes per launch (ncu)",
+                              "traffic": NCU_TRAFFIC_GEMM1_T8192["bytes"], "traffic_unit": "bytes per launch",
+                              "traffic_source": NCU_TRAFFIC_GEMM1_T8192,
                               "algorithmic_bytes": int(256 * (1048576 + 131072 + 4096) + T * 2048 * 2 + T * 8 * 512 * 2)}
         result["stages_ms"] = {k: round(v, 4) for k, v in stage_ms.items()}
         result["stages_tflops"] = {"gemm1": round(ach, 1),
                                    "gemm2": round(flops2 / (stage_ms["gemm2_down"] * 1e-3) / 1e12, 1),
                                    "routed_total": round((flops1 + flops2) / ((stage_ms["gemm1_gate_up_swiglu"] +
                                                                                 stage_ms["gemm2_down"]) * 1e-3) / 1e12, 1)}
+        if not args.no_sweep:
+            # the other points of the prefill curve (same layer, fresh seeded tokens); T=65536 is the one-GPU
+            # baseline of the expert-parallel workload
+            for t_, st_ in ((1024, max(args.steps, 5)), (32768, 5), (65536, 3)):
+                result[f"prefill_T{t_}"] = prefill_point(torch, ops, synth, blk, banks, t_, peaks, st_, seed=100 + t_)
         del d, banks, blk
         torch.cuda.empty_cache()
         if not args.no_decode:
@@ -381,7 +514,7 @@ def run_ours(args) -> None:
         if not args.no_cache:
             result["cache"] = cache_bench(torch)
         if not args.no_cpu:
-            result["cpu_baseline"] = cpu_baseline(256, os.cpu_count() or 1)
+            result["cpu_baseline"] = cpu_baseline(CPU_TOKENS, os.cpu_count() or 1)
     if rank == 0:
         print(json.dumps(result))
     if dist is not None:
@@ -398,6 +531,8 @@ def main() -> None:
     ap.add_argument("--no-decode", action="store_true", help="skip the decode micro-benchmark block")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-cache", action="store_true", help="skip the slot-cache offload workload")
+    ap.add_argument("--no-sweep", action="store_true", help="skip the T=1024/32768/65536 prefill points")
+    ap.add_argument("--no-balanced", action="store_true", help="N>1: skip the balanced-placement figure")
     ap.add_argument("--only-decode", action="store_true", help="run only the decode micro-benchmark (profiling aid)")
     ap.add_argument("--decode-layers", type=int, default=40, help="distinct layer banks in the decode stack")
     ap.add_argument("--decode-reps", type=int, default=20)

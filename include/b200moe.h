@@ -183,7 +183,9 @@ int b200moe_set_pdl(int enable);
  * (freetoken/python/freetoken/layers/moe.py:286-339 with offload_cache.py:1288-1302,1471-1533); this is its native form.
  * create/destroy own the CUDA events; the step call allocates nothing on the device and never blocks on the GPU.
  *   host_tables->stats, when not null, is [L, 3] (one row per layer);
- *   routing_host [L, M, top_k] expert ids; slots_host_pinned / slots_dev [L, M, top_k] receive the slot ids;
+ *   routing_host [L, M, top_k] expert ids; slots_host_pinned / slots_dev [L, M, top_k] receive the slot ids:
+ *   the call writes slots_host_pinned on the host and enqueues an asynchronous copy from it, so the buffer must
+ *   stay untouched until that copy has run on `compute_stream` (give every step in flight its own buffer);
  *   weights_dev: router weights [M, top_k] per layer (stride in elements, 0 = shared by all layers);
  *   dense: array of per-layer dense weights (stride in bytes, 0 = shared); out: [M, H] per layer (stride in bytes);
  *   miss_src / miss_dst [L, M*top_k] and miss_count [L] (may be null) receive the ordered miss plan. */
@@ -239,8 +241,6 @@ int b200moe_sum_routes(const void* in, void* out, int T, int top_k, int H, void*
  * from their owners (no counterpart in the reference, which has no expert parallelism). */
 int b200moe_combine_routes(const void* ic3, const int32_t* topk_ids, int num_slots, int T, int top_k, int H,
                            const void* shared, const void* shared_gate_logit, void* out, void* stream);
-/* Byte offset of the per-route output rows ic3 [T*top_k, H] bf16 inside the prefill workspace (valid after
- * stages PLAN|GEMM1|GEMM2).  Rows of dropped routes are not written. */
 /* Expert-parallel prefill, the part that runs on the expert's owner (no counterpart in the reference, which has
  * no expert parallelism): the two grouped GEMMs over a slice of the box's tokens (x [T, H], already in local
  * memory; its rows are global tokens first_token, first_token + 1, ... modulo world * tokens_per_rank, so a slice
@@ -254,6 +254,8 @@ int b200moe_prefill_ep_routes(const void* x, const b200moe_banks* local_banks, c
                               const int32_t* local_ids, int T, int first_token, int top_k, void* const* peer_ic3,
                               int world, int tokens_per_rank, void* workspace, int64_t workspace_bytes,
                               int32_t* status, void* stream);
+/* Byte offset of the per-route output rows ic3 [T*top_k, H] bf16 inside the prefill workspace (valid after
+ * stages PLAN|GEMM1|GEMM2).  Rows of dropped routes are not written. */
 int64_t b200moe_prefill_ic3_offset(int T, int top_k, int hidden, int intermediate, int num_slots);
 
 #ifdef __cplusplus

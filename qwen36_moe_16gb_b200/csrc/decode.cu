@@ -9,6 +9,8 @@
 // more than 2^28 below the row maximum).  Because any permutation of k applied to both operands leaves
 // a dot product unchanged, fragments take k in load order and no shuffle is needed.
 #include <algorithm>
+#include <mutex>
+#include <utility>
 #include <vector>
 
 #include "common.cuh"
@@ -161,7 +163,7 @@ constexpr int G1_WARPS = 8;
 
 template <int KS>
 B200MOE_DEVICE void decode_gemm1_body(unsigned char* smem_raw, int bx, int r, const __nv_bfloat16* __restrict__ x,
-                                      const b200moe_banks& bk, const int32_t* __restrict__ ids,
+                                      const b200moe_banks& bk, const int32_t* __restrict__ ids, bool ids_settled,
                                       const __nv_bfloat16* __restrict__ logits, int E, float* __restrict__ topk_w_out,
                                       int32_t* __restrict__ topk_ids_out, int top_k, int NT,
                                       __nv_bfloat16* __restrict__ ic2) {
@@ -178,7 +180,11 @@ B200MOE_DEVICE void decode_gemm1_body(unsigned char* smem_raw, int bx, int r, co
   const int token = r / top_k, kk = r - token * top_k;
   int slot;
   if (ids != nullptr) {
-    slot = ids[r];  // written before any kernel of this sequence started
+    // `ids_settled`: the ids were written before the first kernel of this launch sequence started (the host-planned
+    // offload step copies them in ahead of the layer loop).  Otherwise the previous kernel in the stream may have
+    // produced them (router top-k, slot-cache ensure), and its writes are only visible after the dependency wait.
+    if (!ids_settled) pdl_wait();
+    slot = ids[r];
   } else {
     pdl_wait();  // the logits come from the previous kernel
     if (warp == 0) {
@@ -274,7 +280,8 @@ __global__ void __launch_bounds__(G1_WARPS * 32, 2) decode_gemm1_kernel(
     int top_k, int NT, __nv_bfloat16* __restrict__ ic2) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   pdl_launch_dependents();
-  decode_gemm1_body<KS>(smem_raw, blockIdx.x, blockIdx.y, x, bk, ids, logits, E, topk_w_out, topk_ids_out, top_k, NT, ic2);
+  decode_gemm1_body<KS>(smem_raw, blockIdx.x, blockIdx.y, x, bk, ids, false, logits, E, topk_w_out, topk_ids_out, top_k, NT,
+                        ic2);
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -563,7 +570,7 @@ __global__ void __launch_bounds__(G1_WARPS * 32, 2) decode_stage1_kernel(
   extern __shared__ __align__(16) unsigned char smem_raw[];
   pdl_launch_dependents();
   if ((int)blockIdx.y < routes) {
-    decode_gemm1_body<KS>(smem_raw, blockIdx.x, blockIdx.y, x, bk, ids, nullptr, 0, nullptr, nullptr, top_k, NT, ic2);
+    decode_gemm1_body<KS>(smem_raw, blockIdx.x, blockIdx.y, x, bk, ids, true, nullptr, 0, nullptr, nullptr, top_k, NT, ic2);
   } else {
     const int tile = ((int)blockIdx.y - routes) * gridDim.x + blockIdx.x;
     if (tile < s0.tiles + s1.tiles + s2.tiles) dense_rows_body(smem_raw, tile, x, M, bk.hidden, s0, s1, s2);
@@ -604,6 +611,22 @@ static int decode_shape_ok(int M, int top_k, int H, int I, int SI) {
 }
 
 static int g_use_pdl = 1;
+
+// cudaFuncSetAttribute is per device: remember (kernel, device ordinal) pairs that are done, under a lock.
+static std::mutex g_attr_lock;
+static std::vector<std::pair<const void*, int>> g_attr_done;
+static int smem_attr_once(const void* kernel, int bytes) {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return (int)e;
+  std::lock_guard<std::mutex> guard(g_attr_lock);
+  for (const auto& d : g_attr_done)
+    if (d.first == kernel && d.second == dev) return 0;
+  e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+  if (e != cudaSuccess) return (int)e;
+  g_attr_done.emplace_back(kernel, dev);
+  return 0;
+}
 
 template <typename... KArgs, typename... Args>
 static int launch_k(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args... args) {
@@ -648,11 +671,7 @@ template <int KS>
 static int launch_gemm1_ks(const __nv_bfloat16* x, const b200moe_banks* bk, const int32_t* ids, const __nv_bfloat16* logits,
                            int E, float* w_out, int32_t* ids_out, int M, int top_k, const G1Shape& g, const DecodeWs& ws,
                            cudaStream_t st) {
-  static bool attr_done = false;
-  if (!attr_done) {
-    cudaFuncSetAttribute(decode_gemm1_kernel<KS>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024);
-    attr_done = true;
-  }
+  if (int rc = smem_attr_once(reinterpret_cast<const void*>(&decode_gemm1_kernel<KS>), 100 * 1024)) return rc;
   return launch_k(decode_gemm1_kernel<KS>, dim3(g.ctas_per_route, M * top_k), dim3(G1_WARPS * 32),
                   gemm1_smem(bk->hidden, g.nt, KS), st, x, *bk, ids, logits, E, w_out, ids_out, top_k, g.nt, ws.ic2);
 }
@@ -670,11 +689,7 @@ static int launch_gemm1(const __nv_bfloat16* x, const b200moe_banks* bk, const i
 template <int KS>
 static int launch_stage1_ks(const __nv_bfloat16* x, const b200moe_banks* bk, const int32_t* ids, int M, int top_k,
                             const G1Shape& g, const DecodeWs& ws, const b200moe_dense* dense, cudaStream_t st) {
-  static bool attr_done = false;
-  if (!attr_done) {
-    cudaFuncSetAttribute(decode_stage1_kernel<KS>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-    attr_done = true;
-  }
+  if (int rc = smem_attr_once(reinterpret_cast<const void*>(&decode_stage1_kernel<KS>), 200 * 1024)) return rc;
   DenseSeg s[3];
   dense_segments(dense, ws.logits, ws, s);
   const int routes = M * top_k, dense_tiles = s[0].tiles + s[1].tiles + s[2].tiles;
@@ -704,11 +719,7 @@ static int launch_gemm2(const b200moe_banks* bk, const float* w, const int32_t* 
   while (tpw < M && (H / 16) % (tpw * 2) == 0) tpw *= 2;
   const size_t smem = (size_t)top_k * xs_idx128(I) * 2 + (size_t)xs_idx32(si) * 2 +
                       (size_t)(tpw * top_k * 16 + tpw * SH_WARPS * 16) * 4;
-  static bool attr_done = false;
-  if (!attr_done) {
-    cudaFuncSetAttribute(decode_gemm2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
-    attr_done = true;
-  }
+  if (int rc = smem_attr_once(reinterpret_cast<const void*>(&decode_gemm2_kernel), 160 * 1024)) return rc;
   const int warps = top_k + (with_shared ? SH_WARPS : 0);
   return launch_k(decode_gemm2_kernel, dim3(H / (16 * tpw), M), dim3(warps * 32), smem, st, tpw,
                   (const __nv_bfloat16*)ws.ic2, *bk, w, ids, top_k, (const __nv_bfloat16*)ws.hs,
@@ -740,11 +751,7 @@ static int launch_dense_rows(const __nv_bfloat16* x, const b200moe_dense* dense,
                              const DecodeWs& ws, cudaStream_t st) {
   DenseSeg s[3];
   dense_segments(dense, logits, ws, s);
-  static bool attr_done = false;
-  if (!attr_done) {
-    cudaFuncSetAttribute(dense_rows_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-    attr_done = true;
-  }
+  if (int rc = smem_attr_once(reinterpret_cast<const void*>(&dense_rows_kernel), 200 * 1024)) return rc;
   return launch_k(dense_rows_kernel, dim3(s[0].tiles + s[1].tiles + s[2].tiles), dim3(DENSE_WARPS * 32),
                   dense_smem(hidden, DENSE_WARPS), st, x, M, hidden, s[0], s[1], s[2]);
 }
@@ -810,7 +817,6 @@ extern "C" int b200moe_decode_experts(const void* x, const b200moe_banks* banks,
 static __device__ __align__(256) unsigned char g_static_scratch[B200MOE_STATIC_SCRATCH_BYTES];
 static void* g_static_scratch_addr[64];  // per device ordinal; written once under the lock below
 
-#include <mutex>
 static std::mutex g_static_scratch_lock;
 
 extern "C" int b200moe_decode_experts_static(const void* x, const b200moe_banks* banks, const float* topk_weights,
@@ -930,10 +936,13 @@ struct b200moe_offload {
   // the tables as long as only this object changes them; `seen_step` detects outside changes and rebuilds it.
   std::vector<int32_t> prev, next;  // doubly linked, index S = sentinel
   int64_t seen_step = -1;
+  // scratch of ensure() and of the step's plan, sized once (create) so that the launch path never allocates
+  std::vector<int32_t> q, touched, miss, order, plan_src, plan_dst;
+  std::vector<int> miss_n;
 
   void rebuild_list() {
     const int S = tables.cache_size;
-    std::vector<int32_t> order(S);
+    order.resize(S);
     for (int i = 0; i < S; ++i) order[i] = i;
     std::stable_sort(order.begin(), order.end(), [&](int a, int b) { return tables.usage[a] < tables.usage[b]; });
     prev.assign(S + 1, S);
@@ -966,13 +975,13 @@ struct b200moe_offload {
     if (seen_step != *t.step) rebuild_list();
     const int E = t.num_experts, S = t.cache_size, base = layer * E;
     const int64_t step = *t.step + 1;
-    std::vector<int32_t> q;
-    q.reserve(n_ids);
+    q.clear();
     for (int i = 0; i < n_ids; ++i)
       if (ids[i] >= 0 && ids[i] < E) q.push_back(ids[i]);
     std::sort(q.begin(), q.end());
     q.erase(std::unique(q.begin(), q.end()), q.end());
-    std::vector<int32_t> touched, miss;
+    touched.clear();
+    miss.clear();
     for (int e : q) {
       const int slot = t.slot_for_id[base + e];
       if (slot >= 0) {
@@ -1029,6 +1038,18 @@ extern "C" b200moe_offload* b200moe_offload_create(const b200moe_slot_tables* ho
   o->dst.assign(dst_banks, dst_banks + num_banks);
   o->src.assign(src_banks, src_banks + (size_t)num_banks * host_tables->num_layers);
   o->row_bytes.assign(row_bytes, row_bytes + num_banks);
+  {
+    const size_t cap = 64, L = (size_t)host_tables->num_layers;  // at most 8 tokens x 8 routes per layer
+    o->q.reserve(cap);
+    o->touched.reserve(2 * cap);
+    o->miss.reserve(cap);
+    o->order.reserve((size_t)host_tables->cache_size);
+    o->plan_src.assign(L * cap, 0);
+    o->plan_dst.assign(L * cap, 0);
+    o->miss_n.assign(L, 0);
+    o->prev.reserve((size_t)host_tables->cache_size + 1);
+    o->next.reserve((size_t)host_tables->cache_size + 1);
+  }
   o->filled.resize(lookahead + 1);
   o->done.resize(lookahead + 1);
   for (int i = 0; i <= lookahead; ++i) {
@@ -1070,8 +1091,8 @@ extern "C" int b200moe_offload_decode_step(b200moe_offload* o, const int32_t* ro
   const int n_ids = M * top_k, ring = o->lookahead + 1;
   int64_t bytes = 0;
   // plan every layer on the host first (the policy is sequential, the copies are not)
-  std::vector<int> miss_n(L);
-  std::vector<int32_t> plan_src((size_t)L * n_ids), plan_dst((size_t)L * n_ids);
+  std::vector<int>& miss_n = o->miss_n;
+  std::vector<int32_t>&plan_src = o->plan_src, &plan_dst = o->plan_dst;
   for (int l = 0; l < L; ++l) {
     // stats, when given, are [L, 3]: one row per layer
     rc = o->ensure(l, routing_host + (size_t)l * n_ids, n_ids, slots_host_pinned + (size_t)l * n_ids,

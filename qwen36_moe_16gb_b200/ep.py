@@ -271,9 +271,12 @@ class EpPrefill:
         self.last_stats = None
         self.peer = PeerCombine(dist, x.shape[0], top_k, shape.hidden, x.device)
         self.placement = None
+        self.last_status = torch.zeros(4, dtype=torch.int32, device=x.device)
 
     @classmethod
-    def synthetic(cls, dist, shape, tokens: int, seed: int = 0):
+    def synthetic(cls, dist, shape, tokens: int, seed: int = 0, placement: str = "contiguous"):
+        """``placement``: "contiguous" -- rank r owns experts [r*E/N, (r+1)*E/N) (the stated workload); "balanced" --
+        experts dealt by the route counts of this batch (see :func:`balanced_placement`)."""
         from . import synth
         from .block import MoEBlock
 
@@ -285,21 +288,54 @@ class EpPrefill:
         x = torch.randn(tokens, shape.hidden, generator=g, device=dev).to(torch.bfloat16)
         block = MoEBlock(d["router_w"], d["shared_gate_up"], d["shared_down"], d["shared_gate"], shape.top_k,
                          logit_bias=d["logit_bias"])
-        # Expert placement from the routing of this batch: every rank counts its routes per expert, the counts are
-        # summed over the ranks, and balanced_placement spreads the experts so that the ranks' loads are even.
-        # The banks are synthetic, so a rank simply draws as many experts as it owns.
-        from . import ops
+        epr = shape.num_experts // world
+        if placement == "balanced":
+            # every rank counts its routes per expert, the counts are summed over the ranks, and the experts are
+            # dealt so that the ranks' loads are even
+            from . import ops
 
-        _, ids = ops.fused_topk(x, block.router_logits(x), shape.top_k, True)
-        counts = torch.bincount(ids.reshape(-1).long().clamp_(0, shape.num_experts - 1), minlength=shape.num_experts).float()
-        dist.all_reduce(counts)
-        owner, local = balanced_placement(counts.cpu().tolist(), world)
+            _, ids = ops.fused_topk(x, block.router_logits(x), shape.top_k, True)
+            counts = torch.bincount(ids.reshape(-1).long().clamp_(0, shape.num_experts - 1),
+                                    minlength=shape.num_experts).float()
+            dist.all_reduce(counts)
+            owner, local = balanced_placement(counts.cpu().tolist(), world)
+        else:
+            e = torch.arange(shape.num_experts, dtype=torch.int32)
+            owner, local = torch.div(e, epr, rounding_mode="floor").to(torch.int32), (e % epr).to(torch.int32)
         mine = int((owner == rank).sum())
+        # the banks are synthetic: a rank draws as many experts as it owns
         banks = synth.make_banks(g, shape, num_experts=mine, device=dev)
         self = cls(dist, shape, block, banks, x, shape.top_k)
-        self.placement = (owner.to(dev), local.to(dev))
+        self.placement = (owner.to(dev), local.to(dev)) if placement == "balanced" else None
+        self.owner, self.local = owner, local
+        self.placement_name = placement
         self.experts_here = mine
         return self
+
+    def status_ok(self) -> bool:
+        """True when no rank's grouped GEMM gave up on a bounded wait in the last step (max over the ranks)."""
+        st = self.last_status.to(torch.int32).abs().max().reshape(1).clone()
+        self.dist.all_reduce(st, op=self.dist.ReduceOp.MAX)
+        return int(st) == 0
+
+    def gather_banks_to_host(self):
+        """Every rank's banks, collected on every rank and put in expert-id order on the host (a checker's helper:
+        456 MB for the Qwen shape)."""
+        from . import synth
+
+        world = self.world
+        most = int(torch.bincount(self.owner.long(), minlength=world).max())
+        full = {}
+        for role in synth.ROLES:
+            mine = self.banks[role]
+            pad = torch.zeros((most, *mine.shape[1:]), dtype=mine.dtype, device=mine.device)
+            pad[:mine.shape[0]] = mine
+            wire = pad.view(torch.uint8) if pad.element_size() == 1 else pad   # fp8 travels as bytes
+            parts = [torch.empty_like(wire) for _ in range(world)]
+            self.dist.all_gather(parts, wire)
+            stacked = torch.stack([p_.cpu() for p_ in parts]).view(mine.dtype)  # [world, most, ...]
+            full[role] = stacked[self.owner.long(), self.local.long()].contiguous()
+        return full
 
     def _run(self, x, out=None):
         from . import ops
@@ -307,8 +343,9 @@ class EpPrefill:
         logits = self.block.router_logits(x)
         shared, gate = self.block.shared_parts(x)
         w, ids = ops.fused_topk(x, logits, self.top_k, True)
-        out, _ = ep_prefill_step_peer(self.dist, self.peer, x, w, ids, self.shape.num_experts, self.banks, shared, gate,
-                                      placement=self.placement, out=out)
+        out, self.last_status = ep_prefill_step_peer(self.dist, self.peer, x, w, ids, self.shape.num_experts, self.banks,
+                                                     shared, gate, placement=self.placement, out=out)
+        self.last_routing = (w, ids)
         return out
 
     def step(self):

@@ -308,7 +308,8 @@ class SlotCache:
         assert self._buffer_layer[b] == layer_id, "prefetch_prefill_layer first"
         torch.cuda.current_stream(self.device).wait_event(self._ready[b])
         e = self.num_experts
-        return {n: c[b * e:(b + 1) * e] for n, (_, c) in zip(self.bank_schema, self.banks)}
+        # the per-role cache views work for both layouts (separate banks, or one record per slot)
+        return {n: self.bank_caches[n][b * e:(b + 1) * e] for n in self.bank_schema}
 
     def release_prefill_layer(self, layer_id: int) -> None:
         b = layer_id % 2
@@ -316,6 +317,17 @@ class SlotCache:
         self._buffer_layer[b] = None
 
     # ---- stats ---------------------------------------------------------------------------------------
+    def decode_miss_stats_per_layer(self) -> list[dict]:
+        """Per-layer (active, missing, calls) as the reference's per-layer reader reports them."""
+        rows = self.lru_stats.cpu().tolist()
+        return [{"layer": l, "active": int(a), "missing": int(m), "calls": int(c),
+                 "miss_rate": (m / a) if a else 0.0} for l, (a, m, c) in enumerate(rows)]
+
+    def decode_routing_stats(self) -> dict:
+        """Totals over all layers: distinct experts asked for, misses among them, ensure calls."""
+        active, missing, calls = (int(v) for v in self.lru_stats.sum(0))
+        return {"active": active, "missing": missing, "calls": calls}
+
     def decode_miss_stats(self) -> dict:
         active, missing, calls = (int(v) for v in self.lru_stats.sum(0))
         return {"layer_calls": calls, "active_per_layer": active / calls if calls else 0.0,

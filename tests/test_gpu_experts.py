@@ -208,6 +208,26 @@ def test_prefill_full_size_sampled_parity():
     assert torch.equal((got.float() * 2).to(torch.bfloat16).view(torch.int16), got2.view(torch.int16))
 
 
+@pytest.mark.parametrize("t", [1024, 32768])
+def test_prefill_other_sizes_sampled_parity(t):
+    """The other two sizes of the prefill benchmark (T=1024: many experts with a handful of tokens, half-form
+    tiles; T=32768: tens of full tiles per expert): sampled tokens against the oracle, ids bit-exact."""
+    layer = synth.make_layer(0, t, zipf_alpha=1.1)
+    d = _cuda(layer)
+    logits = synth.router_logits(d["x"], d["router_w"], d["logit_bias"])
+    w, ids = ops.fused_topk_softmax(logits, 8, True)
+    rw, rids = oracle.router_topk(logits.cpu(), 8)
+    assert torch.equal(ids.cpu(), rids)
+    got = ops.prefill_experts(d["x"], _banks(d), w, ids, check_status=True).cpu()
+    sample = torch.randperm(t, generator=torch.Generator().manual_seed(3))[:16]
+    want = oracle.moe_experts_bf16(layer["x"][sample], layer, rw[sample], rids[sample])
+    _assert_parity(got[sample], want, f"T={t} sample")
+    # every token row was written: no row keeps the canary of a poisoned output buffer
+    out = torch.full_like(d["x"], float("nan"))
+    ops.prefill_experts(d["x"], _banks(d), w, ids, out=out, check_status=True)
+    assert not torch.isnan(out.float()).any()
+
+
 def test_record_layout_banks_give_identical_results():
     """Banks whose slots are strided through one contiguous per-expert record (the slot cache's layout)."""
     from qwen36_moe_16gb_b200.kernel import B200Nvfp4MoEKernel, MoEConfig

@@ -47,3 +47,26 @@ def test_offload_stack_matches_policy_oracle_and_direct_compute():
         stack.block.decode_route(stack.x, handle)
         want = stack.block.decode_experts(stack.x, handle, w, routing[steps - 1, layer].view(1, -1).cuda())
         assert torch.equal(res["out"][layer].view(torch.int16), want.view(torch.int16)), layer
+
+
+def test_native_runner_policy_at_full_geometry():
+    """The native step runner's recency-list form of the policy at the benchmark's geometry (40 layers, 256 experts,
+    4603 slots): ordered miss plans of every call and the final tables against the oracle.  Small expert shape, so
+    the host banks stay small; the policy does not depend on it."""
+    shape = synth.Shape(hidden=512, intermediate=512, num_experts=256, top_k=8, shared_intermediate=128)
+    L, S, steps = 40, 4603, 48
+    stack = OffloadDecodeStack(shape, L, S, seed=5)
+    routing = synth.cache_routing(seed=0, steps=steps, layers=L)
+    stack.run(routing)
+    o = oracle.SlotCacheOracle(L, shape.num_experts, S)
+    c = 0
+    for s in range(steps):
+        for layer in range(L):
+            o.ensure(layer, routing[s, layer].numpy())
+            src, dst = stack.miss_log[c]
+            assert src == o.src_indices.tolist() and dst == o.evict_slots.tolist(), (s, layer)
+            c += 1
+    assert np.array_equal(stack.cache.slot_for_id.view(-1).numpy(), o.slot_for_id)
+    assert np.array_equal(stack.cache.id_of_slot.numpy(), o.id_of_slot)
+    assert np.array_equal(stack.cache.usage.numpy(), o.usage) and int(stack.cache.step) == o.step
+    stack.close()
