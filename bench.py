@@ -230,23 +230,49 @@ def decode_microbench(torch, peaks, layers: int = 40, reps: int = 20, token_coun
 
 def cache_bench(torch, steps: int = 512, layers: int = 40, slots: int = 4603) -> dict:
     """Expert-slot offload cache: 40 layers x 256 experts (18.2 GB NVFP4) in pinned host memory, 4603 GPU slots,
-    `steps` decode steps at M=1 with Zipf(1.1) routing and 70 % reuse of the previous step's experts."""
+    `steps` decode steps at M=1 with Zipf(1.1) routing and 70 % reuse of the previous step's experts; every layer
+    has its own router and shared-expert weights.  Three forms of the same workload:
+      host_planned_lookahead16  the routing of the whole step is known on the host; fills run up to 16 layers ahead
+      host_planned_lookahead1   fills of layer L overlap layer L-1 only
+      device_routed             nothing is known before a layer runs: device LRU + device gather of the misses,
+                                overlapped with the layer's own shared expert, 40 layers in one CUDA graph"""
     from qwen36_moe_16gb_b200 import synth
+    from qwen36_moe_16gb_b200.decode_overlap import DeviceRoutedDecodeStack
     from qwen36_moe_16gb_b200.offload_runner import OffloadDecodeStack
 
     t0 = time.perf_counter()
-    stack = OffloadDecodeStack(synth.QWEN36, layers, slots)
+    stack = OffloadDecodeStack(synth.QWEN36, layers, slots, per_layer_dense=True)
     setup_s = time.perf_counter() - t0
     routing = synth.cache_routing(seed=0, steps=steps, layers=layers)
-    stack.run(routing[:8])                       # warm-up (also warms the cache, as a served model would be)
-    warm_misses = stack.cache.decode_miss_stats()
-    stack.cache.reset_stats()
-    res = stack.run(routing)
-    out = {k: (round(v, 4) if isinstance(v, float) else v) for k, v in res.items() if k != "out"}
-    out["policy_bit_exact"] = cache_policy_check(stack, routing, warm=8)
+
+    def host_planned(st):
+        st.run(routing[:8])                       # warm-up (also warms the cache, as a served model would be)
+        st.cache.reset_stats()
+        res = st.run(routing)
+        r = {k: (round(v, 4) if isinstance(v, float) else v) for k, v in res.items() if k != "out"}
+        r["policy_bit_exact"] = cache_policy_check(st, routing, warm=8)
+        return r
+
+    out = host_planned(stack)
+    out["form"] = "host_planned_lookahead16"
+    one = OffloadDecodeStack(synth.QWEN36, layers, slots, lookahead=1, records=stack.records, per_layer_dense=True)
+    out["host_planned_lookahead1"] = host_planned(one)
+    one.close()
+    del one
+    torch.cuda.empty_cache()
+    dev_stack = DeviceRoutedDecodeStack(synth.QWEN36, layers, slots, stack.records, dense_blocks=stack.blocks)
+    ids_buf = torch.zeros((layers, 1, synth.QWEN36.top_k), dtype=torch.int32, device="cuda")
+    dev_stack.capture(stack.x, ids_buf)
+    dev_stack.run(routing[:8], ids_buf)
+    dev_stack.cache.reset_stats()
+    res = dev_stack.run(routing, ids_buf)
+    out["device_routed"] = {k: (round(v, 4) if isinstance(v, float) else v) for k, v in res.items() if k != "plans"}
     out.update(layers=layers, slots=slots, host_bank_gb=round(layers * 256 * synth.QWEN36.expert_bytes / 1e9, 3),
-               setup_s=round(setup_s, 1), routing="Zipf(1.1), 70% reuse, seed 0", plan="host LRU + cudaMemcpyAsync on a copy stream")
-    del stack
+               setup_s=round(setup_s, 1), routing="Zipf(1.1), 70% reuse, seed 0", dense_weights="one set per layer",
+               plan="host LRU + cudaMemcpyAsync on a copy stream (host-planned forms); device LRU kernel + gather kernel "
+                    "reading the pinned bank (device-routed form)")
+    stack.close()
+    del stack, dev_stack
     torch.cuda.empty_cache()
     return out
 

@@ -42,6 +42,15 @@ int b200moe_abi_version(void);
 const char* b200moe_build_id(void);
 const char* b200moe_error_string(int code);
 
+/* ---- host banks ---------------------------------------------------------------------------------
+ * Pin-after-fill for the host expert banks: register an already filled, page-aligned host buffer as portable +
+ * mapped, and look up the address a kernel must use to read it (equal to the host address under unified
+ * addressing).  Replaces host_register / host_device_ptr of the reference's pinned-memory extension
+ * (freetoken/python/freetoken/kernel/pinned.py:52-68; used by freetoken/python/freetoken/moe/host_banks.py:137-151). */
+int b200moe_host_register(void* addr, int64_t nbytes);
+int b200moe_host_unregister(void* addr);
+int b200moe_host_device_ptr(void* host_addr, void** device_addr);
+
 /* ---- router: fp32 softmax + top-k + renormalise ------------------------------------------------
  * Replaces fused_topk_softmax (freetoken/python/freetoken/kernel/triton/moe_router.py:109-157).
  * logits [T, E] bf16 (dtype 0) or f32 (dtype 1), row stride in elements; E <= 512.
@@ -162,6 +171,12 @@ int b200moe_decode_block_route(const void* x, const b200moe_dense* dense, int M,
                                void* logits_out, float* topk_weights, int32_t* topk_ids, void* workspace,
                                int64_t workspace_bytes, void* stream);
 /* Stage B: routed experts + shared expert + merge  out = bf16(routed + bf16(shared * bf16(sigmoid(g)))). */
+/* The dense rows of a decode layer by segment (bit 0: router logits -> logits_out [M, E] bf16; bit 1: shared
+ * gate_up -> workspace; bit 2: shared gate logit -> workspace).  Lets a caller run the router first, hand the ids
+ * to the slot cache, and compute the shared expert's rows while the miss fills run on another stream
+ * (freetoken/python/freetoken/decode_overlap.py:44-59, freetoken/python/freetoken/layers/moe.py:286-302). */
+int b200moe_decode_dense_rows(const void* x, const b200moe_dense* dense, int M, int hidden, int segment_mask,
+                              void* logits_out, void* workspace, int64_t workspace_bytes, void* stream);
 int b200moe_decode_block_experts(const void* x, const b200moe_banks* banks, const b200moe_dense* dense,
                                  const float* topk_weights, const int32_t* topk_ids, int M, int top_k, void* out,
                                  void* workspace, int64_t workspace_bytes, void* stream);
@@ -236,6 +251,14 @@ int b200moe_silu_and_mul(const void* in, void* out, int rows, int D, void* strea
 int b200moe_shared_epilogue(const void* routed, const void* shared, const void* gate, void* out, int T, int H,
                             void* stream);
 int b200moe_sum_routes(const void* in, void* out, int T, int top_k, int H, void* stream);
+/* The decoder layer's glue around the block: residual add fused with the RMSNorm that feeds it
+ * (freetoken/python/freetoken/models/qwen3_5_moe/model.py:63-77; kernel semantics of
+ * freetoken/python/freetoken/kernel/triton/norm.py:44-111): z = f32(x) + f32(residual); residual = bf16(z);
+ * x = bf16(z * rsqrt(mean(z^2) + eps) * (w + plus_one)).  rmsnorm is the form without a residual (out-of-place). */
+int b200moe_fused_add_rmsnorm(void* x, void* residual, const void* weight, float eps, int plus_one, int64_t rows, int H,
+                              void* stream);
+int b200moe_rmsnorm(const void* x, const void* weight, void* out, float eps, int plus_one, int64_t rows, int H,
+                    void* stream);
 /* sum_routes that skips routes whose id is outside [0, num_slots) (topk_ids may be null = keep all) and can
  * fuse the merge with the shared expert; used by expert-parallel prefill after the per-route rows came back
  * from their owners (no counterpart in the reference, which has no expert parallelism). */

@@ -303,6 +303,24 @@ def moe_block(layer: dict[str, torch.Tensor], top_k: int, logits: torch.Tensor |
             "shared": shared, "shared_gate_logit": gate, "out": out}
 
 
+def fused_add_rmsnorm(x: torch.Tensor, residual: torch.Tensor, weight: torch.Tensor, eps: float = 1e-6,
+                      plus_one: bool = False) -> tuple[torch.Tensor, torch.Tensor]:
+    """``_fused_add_rmsnorm_kernel`` (``freetoken/python/freetoken/kernel/triton/norm.py:78-111``): ``z = f32(x) +
+    f32(residual)``; new residual ``bf16(z)``; output ``bf16(z * rsqrt(mean(z*z) + eps) * (w [+ 1]))`` -- the norm
+    uses the unrounded sum.  Returns (normed, residual), both bf16."""
+    z = x.float() + residual.float()
+    w = weight.float() + (1.0 if plus_one else 0.0)
+    inv = torch.rsqrt((z * z).mean(dim=-1, keepdim=True) + eps)
+    return (z * inv * w).to(BF16), z.to(BF16)
+
+
+def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float = 1e-6, plus_one: bool = False) -> torch.Tensor:
+    """``_rmsnorm_kernel`` (``freetoken/python/freetoken/kernel/triton/norm.py:44-75``)."""
+    z = x.float()
+    w = weight.float() + (1.0 if plus_one else 0.0)
+    return (z * torch.rsqrt((z * z).mean(dim=-1, keepdim=True) + eps) * w).to(BF16)
+
+
 def error_metrics(got: torch.Tensor, want: torch.Tensor) -> tuple[float, float]:
     """(max-abs, rel-L2) of ``got`` against ``want`` in fp64."""
     g, w = got.double(), want.double()
@@ -311,4 +329,4 @@ def error_metrics(got: torch.Tensor, want: torch.Tensor) -> tuple[float, float]:
 
 __all__ = ["E2M1_VALUES", "router_topk", "align_sizes", "align_block_size", "sorted_routes", "SlotCacheOracle",
            "dequant_nvfp4", "silu_mul", "moe_experts_fp32", "moe_experts_bf16", "shared_expert",
-           "shared_epilogue", "moe_block", "error_metrics"]
+           "shared_epilogue", "moe_block", "fused_add_rmsnorm", "rmsnorm", "error_metrics"]

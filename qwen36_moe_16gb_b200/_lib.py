@@ -40,6 +40,9 @@ SIGNATURES = {
     "b200moe_abi_version": (c_int, []),
     "b200moe_build_id": (C.c_char_p, []),
     "b200moe_error_string": (C.c_char_p, [c_int]),
+    "b200moe_host_register": (c_int, [c_void_p, c_i64]),
+    "b200moe_host_unregister": (c_int, [c_void_p]),
+    "b200moe_host_device_ptr": (c_int, [c_void_p, P(c_void_p)]),
     "b200moe_router_topk": (c_int, [c_void_p, c_int, c_i64, c_int, c_int, c_int, c_int, c_void_p, c_int, c_void_p,
                                     c_void_p, c_void_p]),
     "b200moe_permute_workspace_bytes": (c_i64, [c_int, c_int]),
@@ -58,6 +61,7 @@ SIGNATURES = {
     "b200moe_decode_experts_static": (c_int, [c_void_p, P(Banks), c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p]),
     "b200moe_decode_block_route": (c_int, [c_void_p, P(Dense), c_int, c_int, c_int, c_void_p, c_void_p, c_void_p,
                                            c_void_p, c_i64, c_void_p]),
+    "b200moe_decode_dense_rows": (c_int, [c_void_p, P(Dense), c_int, c_int, c_int, c_void_p, c_void_p, c_i64, c_void_p]),
     "b200moe_decode_block_experts": (c_int, [c_void_p, P(Banks), P(Dense), c_void_p, c_void_p, c_int, c_int, c_void_p,
                                              c_void_p, c_i64, c_void_p]),
     "b200moe_decode_block": (c_int, [c_void_p, P(Banks), P(Dense), c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
@@ -73,6 +77,8 @@ SIGNATURES = {
                                         c_void_p, c_void_p, c_i64, c_void_p, c_void_p]),
     "b200moe_prefill_stages": (c_int, [c_void_p, P(Banks), c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p,
                                        c_void_p, c_void_p, c_i64, c_void_p, c_int, c_void_p]),
+    "b200moe_fused_add_rmsnorm": (c_int, [c_void_p, c_void_p, c_void_p, C.c_float, c_int, c_i64, c_int, c_void_p]),
+    "b200moe_rmsnorm": (c_int, [c_void_p, c_void_p, c_void_p, C.c_float, c_int, c_i64, c_int, c_void_p]),
     "b200moe_silu_and_mul": (c_int, [c_void_p, c_void_p, c_int, c_int, c_void_p]),
     "b200moe_shared_epilogue": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p]),
     "b200moe_sum_routes": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),

@@ -70,6 +70,22 @@ class MoEBlock:
         return ops.prefill_experts(x, bank_tensors, w, ids, shared=shared, shared_gate_logit=gate)
 
 
+class DecoderLayerMoE:
+    """The part of a decoder layer around the block: the mixer's output joins the residual stream and is normalised
+    in one kernel, then the MoE block runs (``Qwen3_5DecoderLayer.forward``,
+    ``freetoken/python/freetoken/models/qwen3_5_moe/model.py:63-77``: ``post_attention_layernorm.forward_add_residual``
+    followed by ``mlp.forward``).  Returns ``(hidden, residual)`` like the reference layer: the block's output is added
+    to the residual by the NEXT layer's fused norm."""
+
+    def __init__(self, block: MoEBlock, post_attention_norm_weight: torch.Tensor, eps: float = 1e-6):
+        self.block, self.weight, self.eps = block, post_attention_norm_weight, eps
+
+    def forward(self, mixer_out: torch.Tensor, residual: torch.Tensor, bank_tensors: dict[str, torch.Tensor],
+                is_prefill: bool | None = None):
+        ops.fused_add_rmsnorm(mixer_out, residual, self.weight, self.eps)   # in place: both tensors are rewritten
+        return self.block.forward(mixer_out, bank_tensors, is_prefill), residual
+
+
 class HostPipeline:
     """Feeds a device step from host memory and returns its result to host memory, step after step, with the
     copies off the compute stream: the host->device copy of step i+1 and the device->host copy of step i-1 run
@@ -116,4 +132,4 @@ class HostPipeline:
         main.wait_stream(self.s_out)
 
 
-__all__ = ["MoEBlock", "HostPipeline"]
+__all__ = ["MoEBlock", "DecoderLayerMoE", "HostPipeline"]

@@ -10,7 +10,7 @@ import sys
 HERE = pathlib.Path(__file__).resolve().parent
 CSRC = HERE / "csrc"
 LIB = HERE / "libb200moe.so"
-SOURCES = ("api.cu", "routing.cu", "slot_cache.cu", "decode.cu", "prefill.cu")
+SOURCES = ("api.cu", "routing.cu", "slot_cache.cu", "decode.cu", "prefill.cu", "glue.cu")
 HEADERS = (CSRC / "common.cuh", CSRC / "router.cuh", HERE.parent / "include" / "b200moe.h")
 
 

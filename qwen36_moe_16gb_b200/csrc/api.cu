@@ -25,3 +25,22 @@ extern "C" const char* b200moe_error_string(int code) {
   if (code > 0) return cudaGetErrorString(static_cast<cudaError_t>(code));
   return "b200moe: unknown error code";
 }
+
+// ---- host banks: page-lock a filled host buffer and look up the address the GPU reads it at ----------------
+extern "C" int b200moe_host_register(void* addr, int64_t nbytes) {
+  if (!addr || nbytes <= 0) return B200MOE_E_NULL;
+  const cudaError_t e = cudaHostRegister(addr, (size_t)nbytes, cudaHostRegisterPortable | cudaHostRegisterMapped);
+  return e == cudaSuccess ? 0 : (int)e;
+}
+
+extern "C" int b200moe_host_unregister(void* addr) {
+  if (!addr) return B200MOE_E_NULL;
+  const cudaError_t e = cudaHostUnregister(addr);
+  return e == cudaSuccess ? 0 : (int)e;
+}
+
+extern "C" int b200moe_host_device_ptr(void* host_addr, void** device_addr) {
+  if (!host_addr || !device_addr) return B200MOE_E_NULL;
+  const cudaError_t e = cudaHostGetDevicePointer(device_addr, host_addr, 0);
+  return e == cudaSuccess ? 0 : (int)e;
+}

@@ -748,9 +748,12 @@ static void dense_segments(const b200moe_dense* dense, __nv_bfloat16* logits, co
 }
 
 static int launch_dense_rows(const __nv_bfloat16* x, const b200moe_dense* dense, int M, int hidden, __nv_bfloat16* logits,
-                             const DecodeWs& ws, cudaStream_t st) {
+                             const DecodeWs& ws, cudaStream_t st, int segment_mask = 7) {
   DenseSeg s[3];
   dense_segments(dense, logits, ws, s);
+  for (int i = 0; i < 3; ++i)
+    if (!(segment_mask & (1 << i))) s[i].tiles = 0;  // a segment without tiles is skipped by the tile walk
+  if (s[0].tiles + s[1].tiles + s[2].tiles == 0) return 0;
   if (int rc = smem_attr_once(reinterpret_cast<const void*>(&dense_rows_kernel), 200 * 1024)) return rc;
   return launch_k(dense_rows_kernel, dim3(s[0].tiles + s[1].tiles + s[2].tiles), dim3(DENSE_WARPS * 32),
                   dense_smem(hidden, DENSE_WARPS), st, x, M, hidden, s[0], s[1], s[2]);
@@ -870,6 +873,21 @@ extern "C" int b200moe_decode_block_route(const void* x, const b200moe_dense* de
                              reinterpret_cast<__nv_bfloat16*>(logits_out), ws, st);
   if (rc) return rc;
   return b200moe_router_topk(logits_out, 0, E, M, E, top_k, 1, nullptr, 0, topk_weights, topk_ids, stream);
+}
+
+extern "C" int b200moe_decode_dense_rows(const void* x, const b200moe_dense* dense, int M, int hidden, int segment_mask,
+                                         void* logits_out, void* workspace, int64_t workspace_bytes, void* stream) {
+  if (!x || !dense || !dense->router_w || !dense->shared_gate_up || !dense->shared_gate || !workspace) return B200MOE_E_NULL;
+  if ((segment_mask & 1) && !logits_out) return B200MOE_E_NULL;
+  const int SI = dense->shared_intermediate, E = dense->num_experts;
+  if (M < 1 || M > 8 || hidden % 128 || hidden > 8192 || E < 1 || E > 512 || SI < 1 || (segment_mask & ~7)) return B200MOE_E_SHAPE;
+  if (!aligned16(x) || !aligned16(dense->router_w) || !aligned16(dense->shared_gate_up) || !aligned16(dense->shared_gate))
+    return B200MOE_E_ALIGN;
+  DecodeWs ws = carve_decode_ws(workspace, M, 1, 0, SI);
+  if (workspace_bytes < ws.bytes) return B200MOE_E_WORKSPACE;
+  return launch_dense_rows(reinterpret_cast<const __nv_bfloat16*>(x), dense, M, hidden,
+                           reinterpret_cast<__nv_bfloat16*>(logits_out), ws, reinterpret_cast<cudaStream_t>(stream),
+                           segment_mask);
 }
 
 extern "C" int b200moe_decode_block_experts(const void* x, const b200moe_banks* banks, const b200moe_dense* dense,

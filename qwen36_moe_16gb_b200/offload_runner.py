@@ -14,6 +14,7 @@ import torch
 
 from . import ops, synth
 from .block import MoEBlock
+from .host_banks import HostBank
 from .kernel import B200Nvfp4MoEKernel, MoEConfig
 from .slot_cache import SlotCache
 
@@ -21,10 +22,14 @@ LOOKAHEAD = 16  # upper bound; a small cache gets a shorter look-ahead
 
 
 class OffloadDecodeStack:
-    def __init__(self, shape: synth.Shape, num_layers: int, cache_size: int, device="cuda", seed: int = 0):
+    def __init__(self, shape: synth.Shape, num_layers: int, cache_size: int, device="cuda", seed: int = 0,
+                 lookahead: int = LOOKAHEAD, records=None, per_layer_dense: bool = False):
+        """``lookahead``: how many layers the copy stream may run ahead of the compute stream (1 = a layer's fills
+        overlap the previous layer only).  ``records``: reuse another stack's pinned host banks.
+        ``per_layer_dense``: every layer gets its own router / shared-expert weights (otherwise one set serves all)."""
         self.shape, self.L, self.S = shape, num_layers, cache_size
         self.dev = torch.device(device)
-        self.lookahead = min(LOOKAHEAD, (cache_size - 1) // shape.top_k - 1)  # cache_size > top_k * (lookahead + 1)
+        self.lookahead = min(lookahead, (cache_size - 1) // shape.top_k - 1)  # cache_size > top_k * (lookahead + 1)
         if self.lookahead < 1:
             raise ValueError("slot cache too small for the copy look-ahead")
         cfg = MoEConfig(shape.num_experts, shape.hidden, shape.intermediate, shape.top_k)
@@ -33,26 +38,47 @@ class OffloadDecodeStack:
         # One contiguous record per expert (all six roles back to back): a miss is ONE host-to-device copy.
         g = torch.Generator(device=self.dev).manual_seed(seed)
         rb = SlotCache.record_bytes(layout)
-        records = []
+        build = records is None
+        records = [] if build else records
+        self.host_banks = []
         stage = torch.empty((shape.num_experts, rb), dtype=torch.uint8, device=self.dev)
-        for _ in range(num_layers):
+        for _ in range(num_layers if build else 0):
             dev_banks = synth.make_banks(g, shape, device=self.dev)
             views = SlotCache.record_views(stage, layout)
             for r in synth.ROLES:
                 views[r].copy_(dev_banks[r])
-            h = torch.empty((shape.num_experts, rb), dtype=torch.uint8, pin_memory=True)
-            h.copy_(stage)
-            records.append(h)
+            bank = HostBank((shape.num_experts, rb), torch.uint8)   # lazy pages; filled, then pinned
+            bank.tensor.copy_(stage)
+            bank.pin()
+            self.host_banks.append(bank)
+            records.append(bank.tensor)
             del dev_banks
         del stage
         self.cache = SlotCache(num_layers, shape.num_experts, cache_size, self.dev, layout=layout, host_tables=True)
         self.cache.collect_stats = True
         self.cache.set_record_sources(records)
+        self.records = records
         self.sources = self.cache.bank_sources
         dense = synth.make_layer(seed, 1, shape, with_banks=False)
         d = {k: v.to(self.dev) for k, v in dense.items()}
         self.x = d["x"]
         self.block = MoEBlock(d["router_w"], d["shared_gate_up"], d["shared_down"], d["shared_gate"], shape.top_k)
+        self.blocks, self._dense_array, self._dense_stride = [self.block], None, 0
+        if per_layer_dense:
+            import ctypes as C
+
+            from ._lib import Dense
+
+            gd = torch.Generator(device=self.dev).manual_seed(seed + 77)
+            h, si, e = shape.hidden, shape.shared_intermediate, shape.num_experts
+            self.blocks = [MoEBlock((torch.randn(e, h, generator=gd, device=self.dev) * 0.02).bfloat16(),
+                                    (torch.randn(2 * si, h, generator=gd, device=self.dev) * 0.02).bfloat16(),
+                                    (torch.randn(h, si, generator=gd, device=self.dev) * 0.02).bfloat16(),
+                                    (torch.randn(1, h, generator=gd, device=self.dev) * 0.02).bfloat16(), shape.top_k)
+                           for _ in range(num_layers)]
+            self.block = self.blocks[0]
+            self._dense_array = (Dense * num_layers)(*[b.dense[0] for b in self.blocks])
+            self._dense_stride = C.sizeof(Dense)
         self.handle = ops.make_banks(self.cache.bank_dict())
         self.copy_stream = torch.cuda.Stream(self.dev)
         self.miss_log: list[tuple[list[int], list[int]]] = []
@@ -102,7 +128,8 @@ class OffloadDecodeStack:
         miss_src = torch.zeros((steps, L, k), dtype=torch.int32)
         miss_dst = torch.zeros((steps, L, k), dtype=torch.int32)
         miss_cnt = torch.zeros((steps, L), dtype=torch.int32)
-        banks, dense = self.handle[0], self.block.dense[0]
+        banks = self.handle[0]
+        dense = self._dense_array if self._dense_array is not None else self.block.dense[0]
         ws = self.block._decode_ws(1, self.handle)
         h2d = C.c_int64(0)
         compute = torch.cuda.current_stream(dev)
@@ -114,7 +141,8 @@ class OffloadDecodeStack:
         out_stride = out.stride(0) * 2 if keep_outputs else 0
         for s in range(steps):
             rc = step_fn(handle, ptr(routing[s]), 1, k, ptr(slots_host[s]), ptr(slots_dev[s]), ptr(w_dev), 0, ptr(self.x),
-                         C.byref(banks), C.byref(dense), 0, ptr(out), out_stride, ptr(ws), ws.numel(),
+                         C.byref(banks), dense if self._dense_array is not None else C.byref(dense), self._dense_stride,
+                         ptr(out), out_stride, ptr(ws), ws.numel(),
                          ptr(miss_src[s]) if log_misses else None, ptr(miss_dst[s]) if log_misses else None,
                          ptr(miss_cnt[s]), C.byref(h2d), self.copy_stream.cuda_stream, compute.cuda_stream)
             if rc:

@@ -144,6 +144,18 @@ def decode_block_route(x, dense: tuple[Dense, tuple], top_k: int, ws: torch.Tens
     return logits, w, ids
 
 
+def decode_dense_rows(x, dense: tuple[Dense, tuple], segment_mask: int, ws: torch.Tensor, logits=None):
+    """The dense rows of a decode layer by segment (1: router logits, returned; 2: shared gate_up and 4: shared gate
+    logit, both left in ``ws`` for :func:`decode_block_experts`)."""
+    d, _ = dense
+    m, h = x.shape
+    if logits is None and (segment_mask & 1):
+        logits = torch.empty((m, d.num_experts), dtype=torch.bfloat16, device=x.device)
+    check(lib().b200moe_decode_dense_rows(ptr(x), C.byref(d), m, h, segment_mask, ptr(logits), ptr(ws), ws.numel(),
+                                          stream_ptr()), "b200moe_decode_dense_rows")
+    return logits
+
+
 def decode_block_experts(x, banks: tuple[Banks, tuple], dense: tuple[Dense, tuple], w, ids, ws, out=None):
     b, _ = banks
     d, _ = dense
@@ -218,6 +230,26 @@ def shared_epilogue(routed, shared, gate):
     out = torch.empty_like(routed)
     check(lib().b200moe_shared_epilogue(ptr(routed), ptr(shared.contiguous()), ptr(gate.contiguous()), ptr(out), t, h,
                                         stream_ptr()), "b200moe_shared_epilogue")
+    return out
+
+
+def fused_add_rmsnorm(x: torch.Tensor, residual: torch.Tensor, weight: torch.Tensor, eps: float = 1e-6,
+                      plus_one: bool = False) -> None:
+    """In place: ``residual += x`` (rounded once to bf16), ``x = rmsnorm(residual_fp32) * (weight [+ 1])``."""
+    _need_cuda(x, residual, weight)
+    assert x.dtype == torch.bfloat16 and x.is_contiguous() and residual.is_contiguous() and x.shape == residual.shape
+    rows, h = x.reshape(-1, x.shape[-1]).shape
+    check(lib().b200moe_fused_add_rmsnorm(ptr(x), ptr(residual), ptr(weight), float(eps), int(plus_one), rows, h,
+                                          stream_ptr()), "b200moe_fused_add_rmsnorm")
+
+
+def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float = 1e-6, plus_one: bool = False, out=None) -> torch.Tensor:
+    _need_cuda(x, weight)
+    assert x.dtype == torch.bfloat16 and x.is_contiguous()
+    rows, h = x.reshape(-1, x.shape[-1]).shape
+    out = torch.empty_like(x) if out is None else out
+    check(lib().b200moe_rmsnorm(ptr(x), ptr(weight), ptr(out), float(eps), int(plus_one), rows, h, stream_ptr()),
+          "b200moe_rmsnorm")
     return out
 
 

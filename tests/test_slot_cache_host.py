@@ -73,3 +73,20 @@ def test_more_misses_than_slots_and_negative_ids():
     assert ids.tolist() == want.tolist() and ids[1] == -1
     with pytest.raises(ValueError):
         SlotCache(1, 8, 4, device="cpu", host_tables=True)  # cache_size < num_experts
+
+
+def test_host_bank_is_lazy_page_aligned_and_views_exactly():
+    """HostBank: page-aligned anonymous mapping, zero until written, a torch view of exactly the asked shape;
+    pageable until pinned (pinning itself needs a GPU and is covered by the offload-stack tests)."""
+    from qwen36_moe_16gb_b200.host_banks import HostBank, HostResidency
+
+    bank = HostBank((3, 1000), torch.uint8)
+    assert bank.addr % 4096 == 0 and bank.nbytes == 3000
+    assert bank.tensor.shape == (3, 1000) and bank.tensor.dtype == torch.uint8
+    assert int(bank.tensor.sum()) == 0
+    bank.tensor[1].fill_(7)
+    assert bank.tensor.data_ptr() == bank.addr and int(bank.tensor.sum()) == 7000
+    assert bank.residency is HostResidency.PAGEABLE
+    f = HostBank((4, 8), torch.float32, huge_pages=False)
+    f.tensor.copy_(torch.arange(32, dtype=torch.float32).view(4, 8))
+    assert float(f.tensor[3, 7]) == 31.0
