@@ -102,6 +102,14 @@ int b200moe_slot_ensure(const b200moe_slot_tables* t, int layer, const int32_t* 
                         void* stream);
 int b200moe_slot_ensure_host(const b200moe_slot_tables* t, int layer, const int32_t* ids, int n_ids,
                              int32_t* ids_out);
+/* One-layer-ahead speculative prefetch (freetoken/python/freetoken/moe/pregate.py:77-117,197-212): the next layer's
+ * router applied to its post-attention RMSNorm of the residual row (one token), then the first `cap` of the top_k
+ * predictions (score order, ties lower id) that are not resident, padded to `width` with the first of them (with
+ * the top-1 prediction when none misses).  logits [E] f32 and query [width] i32 are outputs; the caller hands
+ * `query` to b200moe_slot_ensure and gathers the plan on a side stream. */
+int b200moe_pregate_predict(const void* residual, const void* norm_w, float eps, const void* gate_w, int64_t gate_stride,
+                            int hidden, int num_experts, const int32_t* slot_row, int cap, int top_k, float* logits,
+                            int32_t* query, int width, void* stream);
 /* whole layer into slots [0,E), position == expert id (offload_kernels.py:296-332). */
 int b200moe_slot_materialize(const b200moe_slot_tables* t, int layer, void* stream);
 

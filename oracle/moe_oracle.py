@@ -321,6 +321,37 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float = 1e-6, plus_one: 
     return (z * torch.rsqrt((z * z).mean(dim=-1, keepdim=True) + eps) * w).to(BF16)
 
 
+def pregate_logits(residual: torch.Tensor, norm_w: torch.Tensor, gate_w: torch.Tensor, eps: float) -> torch.Tensor:
+    """``_pregate_logits_kernel`` (``freetoken/python/freetoken/moe/pregate.py:77-89``): fp32 logits of the next
+    layer's router on ``bf16(rmsnorm(residual) * w)``."""
+    x = residual.float().reshape(-1)
+    inv = 1.0 / torch.sqrt((x * x).sum() / x.numel() + eps)
+    y = (x * inv * norm_w.float()).to(BF16).float()
+    return (gate_w.float() * y.unsqueeze(0)).sum(dim=1)
+
+
+def pregate_select(logits: torch.Tensor, slot_row, cap: int, top_k: int, width: int) -> list[int]:
+    """``_pregate_select_kernel`` (``pregate.py:92-117``): the first ``cap`` of the ``top_k`` predictions (score order,
+    lowest id among equals, NaN ranks last) whose slot is unmapped, padded to ``width`` with the first of them, or
+    with the top-1 prediction when none misses."""
+    v = logits.float().clone()
+    v[v != v] = float("-inf")
+    e = v.numel()
+    out, first, top1 = [], 0, 0
+    for k in range(top_k):
+        best = v.max()
+        win = min(int(torch.nonzero(v == best).reshape(-1)[0]), e - 1)
+        if k == 0:
+            top1 = win
+        if int(slot_row[win]) < 0 and len(out) < cap:
+            if not out:
+                first = win
+            out.append(win)
+        v[win] = float("-inf")
+    pad = first if out else top1
+    return out + [pad] * (width - len(out))
+
+
 def error_metrics(got: torch.Tensor, want: torch.Tensor) -> tuple[float, float]:
     """(max-abs, rel-L2) of ``got`` against ``want`` in fp64."""
     g, w = got.double(), want.double()
@@ -329,4 +360,4 @@ def error_metrics(got: torch.Tensor, want: torch.Tensor) -> tuple[float, float]:
 
 __all__ = ["E2M1_VALUES", "router_topk", "align_sizes", "align_block_size", "sorted_routes", "SlotCacheOracle",
            "dequant_nvfp4", "silu_mul", "moe_experts_fp32", "moe_experts_bf16", "shared_expert",
-           "shared_epilogue", "moe_block", "fused_add_rmsnorm", "rmsnorm", "error_metrics"]
+           "shared_epilogue", "moe_block", "fused_add_rmsnorm", "rmsnorm", "pregate_logits", "pregate_select", "error_metrics"]

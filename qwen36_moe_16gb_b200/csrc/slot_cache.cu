@@ -322,3 +322,113 @@ extern "C" int b200moe_slot_gather(int num_banks, void* const* dst_banks_dev, co
       blocks_per_bank);
   return check_launch();
 }
+
+// ------------------------------------------------------------------------------------------------
+// One-layer-ahead speculative prefetch (pre-gate): which experts will the NEXT layer's router pick, judged
+// from the residual stream that leaves this layer?  (freetoken/python/freetoken/moe/pregate.py:77-117)
+//   logits[e] = sum_h gate_w[e, h] * bf16(residual[h] * rsqrt(mean(residual^2) + eps) * norm_w[h])     (fp32)
+//   query[0 .. width) = the first `cap` of the top_k predictions (score order, ties: lower id; NaN ranks last)
+//   whose slot is unmapped, padded with the first of them -- or with the top-1 prediction when none misses.
+// The query then goes through the unchanged LRU ensure; a wrong prediction costs bus traffic and residency only.
+// ------------------------------------------------------------------------------------------------
+namespace b200moe {
+
+// grid = E / 8, block = 256: warp w of a block -> expert 8 * blockIdx.x + w
+__global__ void __launch_bounds__(256) pregate_logits_kernel(const __nv_bfloat16* __restrict__ residual,
+                                                             const __nv_bfloat16* __restrict__ norm_w,
+                                                             const __nv_bfloat16* __restrict__ gate_w, int64_t gate_stride,
+                                                             float* __restrict__ logits, float eps, int H, int E) {
+  __shared__ float red[8];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  float ss = 0.f;
+  for (int h = tid; h < H; h += 256) {
+    const float v = __bfloat162float(residual[h]);
+    ss += v * v;
+  }
+  ss = warp_sum(ss);
+  if (lane == 0) red[warp] = ss;
+  __syncthreads();
+  float tot = 0.f;
+#pragma unroll
+  for (int w = 0; w < 8; ++w) tot += red[w];
+  const float inv = 1.0f / sqrtf(tot / (float)H + eps);
+  const int e = blockIdx.x * 8 + warp;
+  if (e >= E) return;
+  const __nv_bfloat16* g = gate_w + (int64_t)e * gate_stride;
+  float acc = 0.f;
+  for (int h = lane; h < H; h += 32) {
+    const float y = bf16_round(__bfloat162float(residual[h]) * inv * __bfloat162float(norm_w[h]));
+    acc += __bfloat162float(g[h]) * y;
+  }
+  acc = warp_sum(acc);
+  if (lane == 0) logits[e] = acc;
+}
+
+// one warp; E <= 512
+__global__ void __launch_bounds__(32) pregate_select_kernel(const float* __restrict__ logits, const int32_t* __restrict__ slot_row,
+                                                            int32_t* __restrict__ query, int cap, int E, int top_k, int width) {
+  const int lane = threadIdx.x;
+  float v[16];
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    const int n = i * 32 + lane;
+    float x = n < E ? logits[n] : -INFINITY;
+    if (!(x == x)) x = -INFINITY;
+    v[i] = x;
+  }
+  int count = 0, first = 0, top1 = 0;
+  for (int k = 0; k < top_k; ++k) {
+    // highest value, lowest id among equals (an all -inf tail therefore repeats the lowest id, as the reference does)
+    float best = -INFINITY;
+    int arg = 1 << 30;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const int n = i * 32 + lane;
+      if (n < E && (v[i] > best || (v[i] == best && n < arg))) {
+        best = v[i];
+        arg = n;
+      }
+    }
+#pragma unroll
+    for (int o = 16; o; o >>= 1) {
+      const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oa = __shfl_xor_sync(0xffffffffu, arg, o);
+      if (ob > best || (ob == best && oa < arg)) {
+        best = ob;
+        arg = oa;
+      }
+    }
+    const int win = min(arg, E - 1);
+    if (k == 0) top1 = win;
+    const bool miss = slot_row[win] < 0 && count < cap;
+    if (miss) {
+      if (lane == 0) query[count] = win;
+      if (count == 0) first = win;
+      ++count;
+    }
+#pragma unroll
+    for (int i = 0; i < 16; ++i)
+      if (i * 32 + lane == win) v[i] = -INFINITY;
+  }
+  const int pad = count > 0 ? first : top1;
+  for (int p = count + lane; p < width; p += 32) query[p] = pad;
+}
+
+}  // namespace b200moe
+
+extern "C" int b200moe_pregate_predict(const void* residual, const void* norm_w, float eps, const void* gate_w,
+                                       int64_t gate_stride, int hidden, int num_experts, const int32_t* slot_row, int cap,
+                                       int top_k, float* logits, int32_t* query, int width, void* stream) {
+  if (!residual || !norm_w || !gate_w || !slot_row || !logits || !query) return B200MOE_E_NULL;
+  if (hidden < 1 || num_experts < 8 || num_experts % 8 || num_experts > 512 || top_k < 1 || top_k > num_experts || cap < 0 ||
+      width < 1 || cap > width)
+    return B200MOE_E_SHAPE;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  b200moe::pregate_logits_kernel<<<num_experts / 8, 256, 0, st>>>(
+      reinterpret_cast<const __nv_bfloat16*>(residual), reinterpret_cast<const __nv_bfloat16*>(norm_w),
+      reinterpret_cast<const __nv_bfloat16*>(gate_w), gate_stride, logits, eps, hidden, num_experts);
+  int rc = b200moe::check_launch();
+  if (rc) return rc;
+  b200moe::pregate_select_kernel<<<1, 32, 0, st>>>(logits, slot_row, query, cap, num_experts, top_k, width);
+  return b200moe::check_launch();
+}
