@@ -102,6 +102,14 @@ int b200moe_slot_ensure(const b200moe_slot_tables* t, int layer, const int32_t* 
                         void* stream);
 int b200moe_slot_ensure_host(const b200moe_slot_tables* t, int layer, const int32_t* ids, int n_ids,
                              int32_t* ids_out);
+/* Prefill through the cache: split the experts a chunk routes to (or the whole layer: select_all) into residents
+ * (slot >= first_lru_slot, gathered device-to-device) and misses (fetched from the host bank), both as (buffer row,
+ * source) lists in ascending expert id with counts[2] = {hits, misses}; buffer row = buffer_row0 + expert id.
+ * Replaces mark_selected + prefill_split_compact (freetoken/python/freetoken/moe/offload_kernels.py:63-113) as used by
+ * freetoken/python/freetoken/moe/offload_cache.py:1046-1121,1160-1200.  The lists feed b200moe_slot_gather. */
+int b200moe_prefill_split(const int32_t* topk_ids, int n_ids, const int32_t* slot_row, int num_experts, int first_lru_slot,
+                          int buffer_row0, int select_all, int32_t* hit_dst, int32_t* hit_src, int32_t* miss_dst,
+                          int32_t* miss_src, int64_t* counts, void* stream);
 /* One-layer-ahead speculative prefetch (freetoken/python/freetoken/moe/pregate.py:77-117,197-212): the next layer's
  * router applied to its post-attention RMSNorm of the residual row (one token), then the first `cap` of the top_k
  * predictions (score order, ties lower id) that are not resident, padded to `width` with the first of them (with

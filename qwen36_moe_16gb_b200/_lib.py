@@ -51,6 +51,8 @@ SIGNATURES = {
     "b200moe_slot_reset": (c_int, [P(SlotTables), c_void_p]),
     "b200moe_slot_ensure": (c_int, [P(SlotTables), c_int, c_void_p, c_int, c_void_p, c_void_p]),
     "b200moe_slot_ensure_host": (c_int, [P(SlotTables), c_int, c_void_p, c_int, c_void_p]),
+    "b200moe_prefill_split": (c_int, [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p,
+                                      c_void_p, c_void_p, c_void_p]),
     "b200moe_pregate_predict": (c_int, [c_void_p, c_void_p, C.c_float, c_void_p, c_i64, c_int, c_int, c_void_p, c_int, c_int,
                                         c_void_p, c_void_p, c_int, c_void_p]),
     "b200moe_slot_materialize": (c_int, [P(SlotTables), c_int, c_void_p]),

@@ -432,3 +432,77 @@ extern "C" int b200moe_pregate_predict(const void* residual, const void* norm_w,
   b200moe::pregate_select_kernel<<<1, 32, 0, st>>>(logits, slot_row, query, cap, num_experts, top_k, width);
   return b200moe::check_launch();
 }
+
+// ------------------------------------------------------------------------------------------------
+// Prefill through the cache, selected-experts form: which of the experts a chunk routes to are resident
+// (slot >= first_lru_slot: outside the two prefill buffers) and which must come from the host bank?
+// (freetoken/python/freetoken/moe/offload_cache.py:1160-1200 with offload_kernels.py:63-113: mark_selected +
+// prefill_split_compact.)  Both lists are in ascending expert id; destination rows are buffer rows
+// buffer_row0 + expert (position == expert id inside a buffer).  Reads the slot map only: no usage, no stats.
+// ------------------------------------------------------------------------------------------------
+namespace b200moe {
+
+__global__ void __launch_bounds__(1024) prefill_split_kernel(const int32_t* __restrict__ topk_ids, int n_ids,
+                                                             const int32_t* __restrict__ slot_row, int E, int first_lru_slot,
+                                                             int buffer_row0, int select_all, int32_t* __restrict__ hit_dst,
+                                                             int32_t* __restrict__ hit_src, int32_t* __restrict__ miss_dst,
+                                                             int32_t* __restrict__ miss_src, int64_t* __restrict__ counts) {
+  __shared__ int selected[1024];
+  __shared__ int whit[32], wmiss[32];
+  const int e = threadIdx.x, lane = e & 31, warp = e >> 5;
+  selected[e] = select_all;
+  __syncthreads();
+  if (!select_all)
+    for (int i = e; i < n_ids; i += 1024) {
+      const int id = topk_ids[i];
+      if (id >= 0 && id < E) selected[id] = 1;
+    }
+  __syncthreads();
+  const bool sel = e < E && selected[e];
+  const int slot = e < E ? slot_row[e] : -1;
+  const bool hit = sel && slot >= first_lru_slot, miss = sel && !hit;
+  const unsigned hb = __ballot_sync(0xffffffffu, hit), mb = __ballot_sync(0xffffffffu, miss);
+  if (lane == 0) {
+    whit[warp] = __popc(hb);
+    wmiss[warp] = __popc(mb);
+  }
+  __syncthreads();
+  int hbase = 0, mbase = 0, htot = 0, mtot = 0;
+  for (int w = 0; w < 32; ++w) {
+    if (w < warp) {
+      hbase += whit[w];
+      mbase += wmiss[w];
+    }
+    htot += whit[w];
+    mtot += wmiss[w];
+  }
+  const unsigned below = (1u << lane) - 1u;
+  if (hit) {
+    const int i = hbase + __popc(hb & below);
+    hit_dst[i] = buffer_row0 + e;
+    hit_src[i] = slot;
+  }
+  if (miss) {
+    const int i = mbase + __popc(mb & below);
+    miss_dst[i] = buffer_row0 + e;
+    miss_src[i] = e;
+  }
+  if (e == 0) {
+    counts[0] = htot;
+    counts[1] = mtot;
+  }
+}
+
+}  // namespace b200moe
+
+extern "C" int b200moe_prefill_split(const int32_t* topk_ids, int n_ids, const int32_t* slot_row, int num_experts,
+                                     int first_lru_slot, int buffer_row0, int select_all, int32_t* hit_dst, int32_t* hit_src,
+                                     int32_t* miss_dst, int32_t* miss_src, int64_t* counts, void* stream) {
+  if (!slot_row || !hit_dst || !hit_src || !miss_dst || !miss_src || !counts) return B200MOE_E_NULL;
+  if (!select_all && (!topk_ids || n_ids < 0)) return B200MOE_E_NULL;
+  if (num_experts < 1 || num_experts > 1024) return B200MOE_E_SHAPE;
+  b200moe::prefill_split_kernel<<<1, 1024, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      topk_ids, n_ids, slot_row, num_experts, first_lru_slot, buffer_row0, select_all, hit_dst, hit_src, miss_dst, miss_src,
+      counts);
+  return b200moe::check_launch();
+}

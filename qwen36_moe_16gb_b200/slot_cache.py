@@ -39,6 +39,11 @@ class SlotCache:
         self.prefill_overlap, self.prefill_hit_d2d = prefill_overlap, prefill_hit_d2d
         self.layout, self.max_slots = layout, max_slots
         self.host_tables = host_tables
+        # chunks shorter than this move only the experts their router selected (0 = always whole layers)
+        self.prefill_selected_max = 0
+        self.prefill_selected_active = False
+        self.prefill_selected_chunks = 0
+        self.prefill_d2d_rows = self.prefill_h2d_rows = 0
         self.collect_stats = False
         self.decode_shared_overlap = False
         self.layer_major_active = False
@@ -302,6 +307,76 @@ class SlotCache:
             self._ready[b].record(self._copy_stream)
         self._buffer_layer[b] = layer_id
         self.h2d_bytes += self.num_experts * self.expert_bytes
+
+    # ---- selected-experts form and hit/miss split --------------------------------------------------------
+    def select_prefill_route(self, tokens: int) -> None:
+        """Decide, before this chunk's ``begin_prefill``, whether it moves only the experts its router selects
+        (short chunks) instead of whole layers."""
+        self.prefill_selected_active = bool(self.prefill_overlap and not self.host_tables
+                                            and 0 < tokens < self.prefill_selected_max and self._copy_fused_ok)
+        if self.prefill_selected_active:
+            self.prefill_selected_chunks += 1
+
+    def _split_lists(self):
+        if not hasattr(self, "_xfer_lists"):
+            e = self.num_experts
+            self._xfer_lists = [tuple(torch.zeros((e,), dtype=torch.int32, device=self.device) for _ in range(4))
+                                + (torch.zeros((2,), dtype=torch.int64, device=self.device),) for _ in range(2)]
+            self._xfer_event = torch.cuda.Event()
+        return self._xfer_lists
+
+    def _split_and_fill(self, layer_id: int, topk_ids, select_all: bool) -> None:
+        """Residents of ``layer_id`` (slots outside the two buffers) are gathered cache -> buffer on the current
+        stream; the rest come from the host bank on the copy stream (device gather over the pinned bank); the
+        current stream then waits for both.  Reads the slot map only."""
+        b = layer_id % 2
+        e = self.num_experts
+        hit_dst, hit_src, miss_dst, miss_src, counts = self._split_lists()[b]
+        ids = topk_ids.reshape(-1) if topk_ids is not None else None
+        check(lib().b200moe_prefill_split(ptr(ids), 0 if ids is None else ids.numel(), ptr(self.slot_for_id[layer_id]), e,
+                                          2 * e, b * e, int(select_all), ptr(hit_dst), ptr(hit_src), ptr(miss_dst),
+                                          ptr(miss_src), ptr(counts), stream_ptr()), "b200moe_prefill_split")
+        compute = torch.cuda.current_stream(self.device)
+        self._xfer_event.record(compute)
+        with torch.cuda.stream(self._copy_stream):
+            self._copy_stream.wait_event(self._xfer_event)
+            check(lib().b200moe_slot_gather(len(self.banks), ptr(self._dst_dev), ptr(self._src_dev[layer_id]),
+                                            ptr(self._row_bytes_dev), ptr(miss_dst), ptr(miss_src), ptr(counts[1:]), e, 8,
+                                            stream_ptr()), "b200moe_slot_gather")
+            self._ready[b].record(self._copy_stream)
+        # hits: cache rows -> buffer rows of the same tensors (a wide grid: this is an HBM-to-HBM copy)
+        check(lib().b200moe_slot_gather(len(self.banks), ptr(self._dst_dev), ptr(self._dst_dev), ptr(self._row_bytes_dev),
+                                        ptr(hit_dst), ptr(hit_src), ptr(counts[:1]), e, 64, stream_ptr()),
+              "b200moe_slot_gather")
+        compute.wait_event(self._ready[b])
+
+    def selected_prefill_layer(self, layer_id: int, topk_ids: torch.Tensor) -> dict[str, torch.Tensor]:
+        """Fill this layer's buffer with only the experts ``topk_ids`` routes to (after the router) and return its
+        bank views (row == expert id, like the whole-layer path); rows of experts nobody routes to are stale."""
+        assert self.prefill_selected_active, "select_prefill_route first"
+        self._split_and_fill(layer_id, topk_ids, select_all=False)
+        self._buffer_layer[layer_id % 2] = None
+        b, e = layer_id % 2, self.num_experts
+        return {n: self.bank_caches[n][b * e:(b + 1) * e] for n in self.bank_schema}
+
+    def prefetch_prefill_layer_split(self, layer_id: int) -> None:
+        """Whole layer into its buffer with the resident experts copied device-to-device and only the others
+        crossing the bus (``prefill_hit_d2d``)."""
+        b = layer_id % 2
+        if self._buffer_layer[b] == layer_id:
+            return
+        torch.cuda.current_stream(self.device).wait_event(self._released[b])
+        self._copy_stream.wait_event(self._released[b])
+        self._split_and_fill(layer_id, None, select_all=True)
+        self._buffer_layer[b] = layer_id
+
+    def prefill_transfer_stats(self) -> dict:
+        """Rows moved by the last split calls: (device-to-device hits, host-to-device misses) per buffer."""
+        out = {}
+        for b, lists in enumerate(self._split_lists()):
+            hits, misses = (int(v) for v in lists[4].cpu())
+            out[b] = {"d2d_rows": hits, "h2d_rows": misses}
+        return out
 
     def wait_prefill_layer(self, layer_id: int) -> dict[str, torch.Tensor]:
         b = layer_id % 2

@@ -181,3 +181,78 @@ def test_prefill_double_buffer_streams_whole_layers():
         for r in c.bank_schema:
             assert torch.equal(got[r].cpu().view(torch.uint8), src[r][layer].view(torch.uint8)), (layer, r)
     assert c.h2d_bytes == L * E * c.expert_bytes
+
+
+def test_prefill_through_the_cache_feeds_the_grouped_gemm():
+    """Four layers streamed through the two prefill buffers with the grouped GEMM as the consumer, in three forms:
+    whole layers, whole layers with resident experts copied device-to-device, and only the selected experts of a
+    short chunk.  Every layer's output equals the kernels run straight on the layer's full bank; buffer rows hold
+    the host bytes; the hit/miss split counts match the residency."""
+    from qwen36_moe_16gb_b200 import ops, synth
+    from qwen36_moe_16gb_b200.kernel import B200Nvfp4MoEKernel, MoEConfig
+    from qwen36_moe_16gb_b200.offload_layer import OffloadMoELayer
+    from qwen36_moe_16gb_b200.slot_cache import SlotCache
+
+    shape = synth.Shape(hidden=512, intermediate=256, num_experts=16, top_k=4, shared_intermediate=128)
+    L, S, T = 4, 48, 300
+    layout = B200Nvfp4MoEKernel().layout(MoEConfig(shape.num_experts, shape.hidden, shape.intermediate, shape.top_k))
+    g = torch.Generator().manual_seed(21)
+    sources = {r: [] for r in synth.ROLES}
+    for _ in range(L):
+        b = synth.make_banks(g, shape)
+        for r in synth.ROLES:
+            sources[r].append(b[r].pin_memory())
+    x = torch.randn(T, shape.hidden, generator=g).to(torch.bfloat16).cuda()
+    ids = torch.stack([torch.randperm(shape.num_experts, generator=g)[:shape.top_k] for _ in range(T)]).to(torch.int32).cuda()
+    w = torch.rand(T, shape.top_k, generator=g).cuda()
+    want = [ops.prefill_experts(x, {r: sources[r][l].cuda() for r in synth.ROLES}, w, ids, check_status=True).clone()
+            for l in range(L)]
+    for hit_d2d in (False, True):
+        cache = SlotCache(L, shape.num_experts, S, "cuda", prefill_overlap=True, prefill_hit_d2d=hit_d2d, layout=layout)
+        cache.set_bank_sources(sources)
+        for c in cache.bank_caches.values():
+            c.view(torch.uint8).fill_(0xA5)
+        if hit_d2d:
+            # a previous decode left residents: the first 2E slots (the buffers' region) hold layers 3 and 2, then
+            # three experts of layers 0 and 1 sit in slots outside the buffers
+            for l in (3, 2):
+                every = torch.arange(shape.num_experts, dtype=torch.int32, device="cuda")
+                cache.ensure_experts(l, every)
+                cache.copy_missing()
+            for l in (0, 1):
+                warm = torch.tensor([1, 5, 9], dtype=torch.int32, device="cuda")
+                cache.ensure_experts(l, warm)
+                cache.copy_missing()
+            assert int((cache.slot_for_id >= 2 * shape.num_experts).sum()) == 6
+        layers = [OffloadMoELayer(l, shape.num_experts, shape.top_k, cache) for l in range(L)]
+        for l in range(L):
+            got = layers[l].forward(x, w, ids.clone(), is_prefill=True)
+            assert torch.equal(got.view(torch.int16), want[l].view(torch.int16)), (hit_d2d, l)
+            if hit_d2d and l == 0:   # buffers 0 and 1 now hold layers 0 and 1: three residents each came device-to-device
+                torch.cuda.synchronize()
+                st = cache.prefill_transfer_stats()
+                for b in (0, 1):
+                    assert st[b]["d2d_rows"] == 3 and st[b]["h2d_rows"] == shape.num_experts - 3, st
+        torch.cuda.synchronize()
+    # short chunk: only the experts it routes to move
+    cache = SlotCache(L, shape.num_experts, S, "cuda", prefill_overlap=True, layout=layout)
+    cache.set_bank_sources(sources)
+    cache.prefill_selected_max = 64
+    for c in cache.bank_caches.values():
+        c.view(torch.uint8).fill_(0xA5)
+    xs, ws = x[:9].contiguous(), w[:9].contiguous()
+    ids_s = ids[:9].contiguous()
+    ids_s[:, :] = torch.tensor([2, 3, 7, 11], dtype=torch.int32)
+    layers = [OffloadMoELayer(l, shape.num_experts, shape.top_k, cache) for l in range(L)]
+    for l in range(L):
+        ref = ops.prefill_experts(xs, {r: sources[r][l].cuda() for r in synth.ROLES}, ws, ids_s, check_status=True).clone()
+        got = layers[l].forward(xs, ws, ids_s.clone(), is_prefill=True)
+        assert torch.equal(got.view(torch.int16), ref.view(torch.int16)), l
+    torch.cuda.synchronize()
+    assert cache.prefill_selected_chunks == 1
+    st = cache.prefill_transfer_stats()
+    assert st[1]["h2d_rows"] == 4 and st[1]["d2d_rows"] == 0
+    e = shape.num_experts
+    buf = cache.bank_caches["gate_up"][e:2 * e].cpu().view(torch.uint8)      # layer 3 went into buffer 1
+    assert torch.equal(buf[7], sources["gate_up"][3][7].view(torch.uint8))
+    assert bool((buf[0] == 0xA5).all())                                       # an expert nobody routed to stayed untouched

@@ -65,3 +65,26 @@ def test_slot_cache_geometry_errors():
         c.validate_rebuild(4)
     c.rebuild(24)
     assert c.cache_size == 24 and c.id_of_slot.numel() == 24 and int(c.step) == 0
+
+
+def test_plugin_types_agree_with_the_reference_interface_when_it_is_present():
+    """Field-for-field agreement of the mirrored plugin types with the reference's own, read from the reference's
+    source text (its module needs packages that are not installed; skipped where the checkout is absent)."""
+    import ast
+    import dataclasses
+    import pathlib
+
+    src = pathlib.Path("/root/reference/freetoken/python/freetoken/layers/quantization/moe/base.py")
+    if not src.exists():
+        pytest.skip("reference checkout not present")
+    tree = ast.parse(src.read_text())
+    classes = {n.name: n for n in tree.body if isinstance(n, ast.ClassDef)}
+    from qwen36_moe_16gb_b200 import kernel
+
+    for name in ("MoEConfig", "BankSpec", "ExpertView"):
+        theirs = [st.target.id for st in classes[name].body if isinstance(st, ast.AnnAssign) and isinstance(st.target, ast.Name)]
+        ours = [f.name for f in dataclasses.fields(getattr(kernel, name))]
+        assert ours == theirs, (name, ours, theirs)
+    theirs = {st.name for st in classes["MoEKernel"].body if isinstance(st, ast.FunctionDef)}
+    for method in ("unusable_reason", "worth_it", "slot_limit", "layout", "pack", "apply"):
+        assert method in theirs and callable(getattr(kernel.B200Nvfp4MoEKernel, method)), method
