@@ -275,6 +275,18 @@ int b200moe_fused_add_rmsnorm(void* x, void* residual, const void* weight, float
                               void* stream);
 int b200moe_rmsnorm(const void* x, const void* weight, void* out, float eps, int plus_one, int64_t rows, int H,
                     void* stream);
+/* The block's dense bf16 linears on the tensor cores (tcgen05): the router's gate and the shared expert's projections
+ * (freetoken/python/freetoken/models/qwen3_5_moe/moe.py:20-36,66,86,99-106; the reference calls a library GEMM,
+ * freetoken/python/freetoken/layers/quantization/linear/unquantized.py:18-24).
+ *   swiglu == 0: out[T, N] = bf16(x[T, K] . w[N, K]^T + bias[N])        bias fp32 or null; N % 8 == 0
+ *   swiglu == 1: w = [2 * N/2, K] (gate rows, then up rows); out[T, N/2] = bf16(silu(bf16(gate)) * bf16(up)), the
+ *                result of the linear followed by the activation kernel; (N/2) % 64 == 0
+ * K % 64 == 0; x, w, out 16-byte aligned and contiguous.  status: one int32 on the device, set non-zero if a wait
+ * inside the kernel ran out (never in a correct run); the caller zeroes it once.
+ * row_dot: out[T] = bf16(x[T, K] . w[K]) -- the shared expert's scalar gate logit (K % 8 == 0). */
+int b200moe_dense_linear(const void* x, const void* w, const float* bias, void* out, int T, int N, int K, int swiglu,
+                         int32_t* status, void* stream);
+int b200moe_row_dot(const void* x, const void* w, void* out, int T, int K, void* stream);
 /* sum_routes that skips routes whose id is outside [0, num_slots) (topk_ids may be null = keep all) and can
  * fuse the merge with the shared expert; used by expert-parallel prefill after the per-route rows came back
  * from their owners (no counterpart in the reference, which has no expert parallelism). */

@@ -83,6 +83,8 @@ SIGNATURES = {
                                        c_void_p, c_void_p, c_i64, c_void_p, c_int, c_void_p]),
     "b200moe_fused_add_rmsnorm": (c_int, [c_void_p, c_void_p, c_void_p, C.c_float, c_int, c_i64, c_int, c_void_p]),
     "b200moe_rmsnorm": (c_int, [c_void_p, c_void_p, c_void_p, C.c_float, c_int, c_i64, c_int, c_void_p]),
+    "b200moe_dense_linear": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p]),
+    "b200moe_row_dot": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p]),
     "b200moe_silu_and_mul": (c_int, [c_void_p, c_void_p, c_int, c_int, c_void_p]),
     "b200moe_shared_epilogue": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p]),
     "b200moe_sum_routes": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),

@@ -6,8 +6,9 @@ Decode (<= 8 tokens): three launches chained by programmatic dependent launch --
 shared gate_up + gate logit), expert GEMM1 with the router top-k in its prologue + SwiGLU (+ shared activation),
 expert GEMM2 + route sum + shared down + merge.  With the slot cache in between (offload), routing is a separate
 launch so that the LRU can rewrite expert ids to slot ids before the expert kernels.
-Prefill: router logits and the shared expert's two dense bf16 GEMMs go to cuBLAS (plain library GEMMs, as in
-the reference); routing, permutation, the grouped expert GEMMs and the merge are this package's kernels.
+Prefill: router logits and the shared expert's dense bf16 GEMMs (gate_up with its SwiGLU in the epilogue, down) run
+on this package's tcgen05 dense GEMM, like routing, permutation, the grouped expert GEMMs and the merge: no library
+GEMM is on the path.
 """
 from __future__ import annotations
 
@@ -23,6 +24,7 @@ class MoEBlock:
         self.shared_down, self.shared_gate = shared_down, shared_gate
         self.top_k = top_k
         self.logit_bias = logit_bias  # synthetic popularity skew (fp32 [E]); None in a real model
+        self._bias_f32 = None if logit_bias is None else logit_bias.to(torch.bfloat16).float().contiguous()
         self.dense = ops.make_dense(router_w, shared_gate_up, shared_down, shared_gate)
         self._ws = {}
 
@@ -45,15 +47,12 @@ class MoEBlock:
         return ops.decode_block(x, banks, self.dense, self.top_k, self._decode_ws(x.shape[0], banks), out)
 
     def router_logits(self, x):
-        if self.logit_bias is None:
-            return torch.nn.functional.linear(x, self.router_w)
-        # bias added in the GEMM epilogue (fp32) before the single bf16 rounding
-        return torch.nn.functional.linear(x, self.router_w, self.logit_bias.to(torch.bfloat16))
+        # the synthetic bias is added in the GEMM epilogue (fp32) before the single bf16 rounding
+        return ops.dense_linear(x, self.router_w, self._bias_f32)
 
     def shared_parts(self, x):
-        hs = torch.nn.functional.linear(x, self.shared_gate_up)
-        shared = torch.nn.functional.linear(ops.silu_and_mul(hs), self.shared_down)
-        return shared, torch.nn.functional.linear(x, self.shared_gate)
+        act = ops.dense_linear(x, self.shared_gate_up, swiglu=True)
+        return ops.dense_linear(act, self.shared_down), ops.row_dot(x, self.shared_gate)
 
     # ---- whole block ---------------------------------------------------------------------------------
     def forward(self, x: torch.Tensor, bank_tensors: dict[str, torch.Tensor], is_prefill: bool | None = None):

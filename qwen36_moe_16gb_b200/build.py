@@ -10,8 +10,8 @@ import sys
 HERE = pathlib.Path(__file__).resolve().parent
 CSRC = HERE / "csrc"
 LIB = HERE / "libb200moe.so"
-SOURCES = ("api.cu", "routing.cu", "slot_cache.cu", "decode.cu", "prefill.cu", "glue.cu")
-HEADERS = (CSRC / "common.cuh", CSRC / "router.cuh", HERE.parent / "include" / "b200moe.h")
+SOURCES = ("api.cu", "routing.cu", "slot_cache.cu", "decode.cu", "prefill.cu", "glue.cu", "dense.cu")
+HEADERS = (CSRC / "common.cuh", CSRC / "router.cuh", CSRC / "tc.cuh", HERE.parent / "include" / "b200moe.h")
 
 
 def source_digest() -> str:

@@ -253,6 +253,46 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float = 1e-6, plus_one: 
     return out
 
 
+_dense_status: dict = {}
+
+
+def dense_status(device) -> torch.Tensor:
+    """The int32 word the dense GEMM sets when one of its bounded waits ran out (zero in a correct run)."""
+    key = torch.device(device).index if torch.device(device).index is not None else torch.cuda.current_device()
+    if key not in _dense_status:
+        _dense_status[key] = torch.zeros(1, dtype=torch.int32, device=torch.device("cuda", key))
+    return _dense_status[key]
+
+
+def dense_linear(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None, swiglu: bool = False, out=None) -> torch.Tensor:
+    """``bf16(x @ w.T + bias)`` on the tensor cores; with ``swiglu`` the rows of ``w`` are gate rows then up rows and the
+    result is ``silu(gate) * up`` (each half rounded to bf16 first, as the linear followed by the activation gives)."""
+    _need_cuda(x, w)
+    assert x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.is_contiguous() and w.is_contiguous()
+    t, k = x.shape
+    n = w.shape[0]
+    assert w.shape[1] == k
+    if bias is not None:
+        assert bias.dtype == torch.float32 and bias.is_contiguous() and bias.numel() == n
+    cols = n // 2 if swiglu else n
+    out = torch.empty((t, cols), dtype=torch.bfloat16, device=x.device) if out is None else out
+    assert out.is_contiguous() and out.shape == (t, cols)
+    check(lib().b200moe_dense_linear(ptr(x), ptr(w), None if bias is None else ptr(bias), ptr(out), t, n, k, int(swiglu),
+                                     ptr(dense_status(x.device)), stream_ptr()), "b200moe_dense_linear")
+    return out
+
+
+def row_dot(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    """``bf16(x @ w.T)`` for a single weight row: [T, K] x [1, K] -> [T, 1]."""
+    _need_cuda(x, w)
+    assert x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.is_contiguous() and w.is_contiguous()
+    t, k = x.shape
+    assert w.numel() == k
+    out = torch.empty((t, 1), dtype=torch.bfloat16, device=x.device)
+    check(lib().b200moe_row_dot(ptr(x), ptr(w), ptr(out), t, k, stream_ptr()), "b200moe_row_dot")
+    return out
+
+
 def sum_routes(ic3: torch.Tensor) -> torch.Tensor:
     _need_cuda(ic3)
     t, k, h = ic3.shape
