@@ -439,9 +439,9 @@ def run_ours(args) -> None:
         pipe = HostPipeline(run_block, x_host, out_host, dev)
 
         info = {"h2d": x_host.numel() * 2, "d2h": out_host.numel() * 2}
-        # this package's kernels per step: router top-k, 4 permutation, tile list, token gather, 2 grouped GEMMs,
-        # combine, silu_and_mul (the four dense GEMMs of router and shared expert are cuBLAS and not counted)
-        launches_per_step = 11
+        # this package's kernels per step: 3 dense GEMMs (router, shared gate_up + SwiGLU, shared down), gate logit,
+        # router top-k, 4 permutation, tile list, token gather, 2 grouped GEMMs, combine; no library kernel runs
+        launches_per_step = 14
 
     for _ in range(max(args.warmup, 3)):
         step()

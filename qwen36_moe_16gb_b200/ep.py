@@ -259,7 +259,9 @@ def ep_prefill_step_peer(dist, peer: PeerCombine, x, topk_weights, topk_ids, num
 class EpPrefill:
     """Synthetic expert-parallel prefill workload: T tokens per rank, Zipf(1.1) routing, local banks on the GPU."""
 
-    launches_per_step = 10  # router 1, permutation 4, tile list 1, grouped GEMM 2, combine 1, silu_and_mul 1
+    # dense GEMM 3 (router, shared gate_up + SwiGLU, shared down), gate logit 1, router top-k 1, permutation 4,
+    # tile list 1, grouped GEMM 2, combine 1 (the token gather between ranks is extra and depends on the ring)
+    launches_per_step = 13
 
     def __init__(self, dist, shape, block, banks, x, top_k):
         self.dist, self.shape, self.block, self.banks, self.x, self.top_k = dist, shape, block, banks, x, top_k
