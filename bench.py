@@ -315,10 +315,7 @@ def prefill_point(torch, ops, synth, blk, banks, tokens: int, peaks: dict, steps
     out = torch.empty_like(x)
 
     def step():
-        logits = blk.router_logits(x)
-        shared, gate = blk.shared_parts(x)
-        w, ids = ops.fused_topk(x, logits, shape.top_k, True)
-        ops.prefill_experts(x, banks, w, ids, shared=shared, shared_gate_logit=gate, out=out)
+        blk.prefill(x, banks, out=out)
 
     for _ in range(3):
         step()
@@ -423,16 +420,10 @@ def run_ours(args) -> None:
         out_dev = torch.empty_like(x_dev)
 
         def step():
-            logits = blk.router_logits(x_dev)
-            shared, gate = blk.shared_parts(x_dev)
-            w, ids = ops.fused_topk(x_dev, logits, shape.top_k, True)
-            ops.prefill_experts(x_dev, banks, w, ids, shared=shared, shared_gate_logit=gate, out=out_dev)
+            blk.prefill(x_dev, banks, out=out_dev)
 
         def run_block(xd, od):
-            logits = blk.router_logits(xd)
-            shared, gate = blk.shared_parts(xd)
-            w, ids = ops.fused_topk(xd, logits, shape.top_k, True)
-            return ops.prefill_experts(xd, banks, w, ids, shared=shared, shared_gate_logit=gate, out=od)
+            return blk.prefill(xd, banks, out=od)
 
         from qwen36_moe_16gb_b200.block import HostPipeline
 
@@ -526,6 +517,11 @@ def run_ours(args) -> None:
                               "traffic_source": NCU_TRAFFIC_GEMM1_T8192,
                               "algorithmic_bytes": int(256 * (1048576 + 131072 + 4096) + T * 2048 * 2 + T * 8 * 512 * 2)}
         result["stages_ms"] = {k: round(v, 4) for k, v in stage_ms.items()}
+        # the same step with the shared expert on the main stream (no side-stream overlap), for comparison
+        for _ in range(3):
+            blk.prefill(x_dev, banks, out=out_dev, overlap=False)
+        result["ms_per_step_serial"] = round(time_events(lambda: blk.prefill(x_dev, banks, out=out_dev, overlap=False),
+                                                         args.steps, torch), 4)
         result["stages_tflops"] = {"gemm1": round(ach, 1),
                                    "gemm2": round(flops2 / (stage_ms["gemm2_down"] * 1e-3) / 1e12, 1),
                                    "routed_total": round((flops1 + flops2) / ((stage_ms["gemm1_gate_up_swiglu"] +

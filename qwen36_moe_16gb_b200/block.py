@@ -27,6 +27,7 @@ class MoEBlock:
         self._bias_f32 = None if logit_bias is None else logit_bias.to(torch.bfloat16).float().contiguous()
         self.dense = ops.make_dense(router_w, shared_gate_up, shared_down, shared_gate)
         self._ws = {}
+        self._overlap = {}
 
     def _decode_ws(self, m, banks):
         key = (m, banks[0].intermediate, torch.cuda.current_stream().cuda_stream)
@@ -63,10 +64,40 @@ class MoEBlock:
         if decode and t <= DECODE_MAX_TOKENS and self.logit_bias is None and banks[0].hidden % 512 == 0 \
                 and banks[0].intermediate % 512 == 0:
             return self.decode_fused(x, banks)[0]
+        return self.prefill(x, bank_tensors)
+
+    def prefill(self, x: torch.Tensor, bank_tensors: dict[str, torch.Tensor], out=None, overlap: bool = True,
+                check_status: bool = False):
+        """Prefill form of the block.  The shared expert does not depend on the routing, so with ``overlap`` its GEMMs
+        run on a side stream next to the router's top-k and the permutation (small latency-bound kernels that leave the
+        tensor cores idle) and join before the merge -- the prefill counterpart of the decode path's shared-expert
+        overlap (``freetoken/python/freetoken/decode_overlap.py:44-59``).  The side stream's work of one call is ordered
+        after the router GEMM of that call and therefore after the merge of the previous one, so its buffers can be
+        reused call after call."""
         logits = self.router_logits(x)
-        shared, gate = self.shared_parts(x)
+        if not overlap:
+            shared, gate = self.shared_parts(x)
+            w, ids = ops.fused_topk(x, logits, self.top_k, True)
+            return ops.prefill_experts(x, bank_tensors, w, ids, shared=shared, shared_gate_logit=gate, out=out,
+                                       check_status=check_status)
+        main = torch.cuda.current_stream(x.device)
+        side, fork, join = self._overlap_state(x.device)
+        fork.record(main)
+        side.wait_event(fork)
+        with torch.cuda.stream(side):
+            shared, gate = self.shared_parts(x)
+            join.record(side)
         w, ids = ops.fused_topk(x, logits, self.top_k, True)
-        return ops.prefill_experts(x, bank_tensors, w, ids, shared=shared, shared_gate_logit=gate)
+        out = ops.prefill_experts(x, bank_tensors, w, ids, out=out, stages=ops.STAGE_PLAN | ops.STAGE_GEMM1 | ops.STAGE_GEMM2)
+        main.wait_event(join)
+        return ops.prefill_experts(x, bank_tensors, w, ids, shared=shared, shared_gate_logit=gate, out=out,
+                                   stages=ops.STAGE_COMBINE, check_status=check_status)
+
+    def _overlap_state(self, device):
+        key = torch.device(device).index
+        if key not in self._overlap:
+            self._overlap[key] = (torch.cuda.Stream(device), torch.cuda.Event(), torch.cuda.Event())
+        return self._overlap[key]
 
 
 class DecoderLayerMoE:

@@ -301,3 +301,31 @@ def test_host_pipeline_matches_direct_call():
         pipe.join()
         torch.cuda.synchronize()
         assert torch.equal(out_host.view(torch.int16), want.cpu().view(torch.int16))
+
+
+def test_prefill_with_the_shared_expert_on_a_side_stream_is_bit_identical():
+    """The overlapped prefill form (shared expert next to top-k and permutation) returns the serial form's bits, call
+    after call with changing tokens, and also when the whole block is captured in a CUDA graph."""
+    shape = synth.Shape(hidden=1024, intermediate=512, num_experts=16, top_k=4, shared_intermediate=256)
+    layer = synth.make_layer(5, 900, shape, zipf_alpha=1.1)
+    d = {k: v.cuda() for k, v in layer.items()}
+    banks = {r: d[r] for r in synth.ROLES}
+    blk = MoEBlock(d["router_w"], d["shared_gate_up"], d["shared_down"], d["shared_gate"], shape.top_k,
+                   logit_bias=d["logit_bias"])
+    g = torch.Generator(device="cuda").manual_seed(1)
+    xs = [d["x"]] + [torch.randn(900, shape.hidden, generator=g, device="cuda").bfloat16() for _ in range(4)]
+    serial = [blk.prefill(x, banks, overlap=False, check_status=True).clone() for x in xs]
+    for _ in range(3):
+        for x, want in zip(xs, serial):
+            got = blk.prefill(x, banks, check_status=True)
+            assert torch.equal(got.view(torch.int16), want.view(torch.int16))
+    x_buf, out = xs[0].clone(), torch.empty_like(xs[0])
+    blk.prefill(x_buf, banks, out=out)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        blk.prefill(x_buf, banks, out=out)
+    for x, want in zip(xs, serial):
+        x_buf.copy_(x)
+        graph.replay()
+        assert torch.equal(out.view(torch.int16), want.view(torch.int16))

@@ -256,3 +256,34 @@ def test_prefill_through_the_cache_feeds_the_grouped_gemm():
     buf = cache.bank_caches["gate_up"][e:2 * e].cpu().view(torch.uint8)      # layer 3 went into buffer 1
     assert torch.equal(buf[7], sources["gate_up"][3][7].view(torch.uint8))
     assert bool((buf[0] == 0xA5).all())                                       # an expert nobody routed to stayed untouched
+
+
+@pytest.mark.parametrize("per_layer", [True, False])
+def test_banks_loaded_from_files_feed_the_cache_and_the_decode_kernels(per_layer, tmp_path):
+    """Disk -> pinned record banks (`bank_files.load_records`) -> slot cache misses -> expert GEMVs: the result is
+    the one the resident banks give."""
+    from qwen36_moe_16gb_b200 import bank_files, ops
+    from qwen36_moe_16gb_b200.kernel import B200Nvfp4MoEKernel, MoEConfig
+
+    L, E, S, k = 3, 16, 20, 4
+    shape = synth.Shape(hidden=1024, intermediate=512, num_experts=E, top_k=k, shared_intermediate=256)
+    g = torch.Generator().manual_seed(3)
+    layers = [synth.make_banks(g, shape) for _ in range(L)]
+    bank_files.write_expert_banks(str(tmp_path), layers, per_layer=per_layer, shard_limit=1 << 20)
+    layout = B200Nvfp4MoEKernel().layout(MoEConfig(E, shape.hidden, shape.intermediate, k))
+    records, keep = bank_files.load_records(str(tmp_path), L, layout)
+    assert all(b.residency.value == "pinned" for b in keep)
+    cache = SlotCache(L, E, S, DEV, layout=layout)
+    cache.set_record_sources(records)
+    x = (torch.randn(2, shape.hidden, generator=g) * 0.5).bfloat16().to(DEV)
+    w = torch.full((2, k), 1.0 / k, device=DEV)
+    for layer in (0, 2, 1, 2):
+        ids = torch.stack([torch.randperm(E, generator=g)[:k] for _ in range(2)]).to(torch.int32)
+        want = ops.decode_experts(x, {r: t.to(DEV) for r, t in layers[layer].items()}, w, ids.to(DEV))
+        slots = ids.to(DEV)
+        cache.ensure_experts(layer, slots)
+        cache.copy_missing()
+        got = ops.decode_experts(x, cache.bank_dict(), w, slots)
+        assert torch.equal(got.view(torch.int16), want.view(torch.int16))
+    for b in keep:
+        b.unpin()
