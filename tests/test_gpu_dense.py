@@ -103,3 +103,30 @@ def test_block_prefill_path_launches_no_library_gemm():
     assert any("dense_gemm_kernel" in n for n in names), names
     foreign = [n for n in names if "b200moe" not in n and any(s in n.lower() for s in ("nvjet", "cutlass", "cublas", "gemm", "gemv"))]
     assert not foreign, foreign
+
+
+def test_prefill_and_decode_router_logits_agree_to_one_rounding_step():
+    """The prefill GEMM (tcgen05, k in 16-wide steps) and the decode GEMV (warp MMA, k split over lanes) add the same
+    2048 products in different orders: both are within one bf16 step of the fp32 result, their top-8 sets agree
+    wherever the 8th and 9th logits are further apart than that step, and most logits are bit-identical."""
+    from qwen36_moe_16gb_b200 import ops, synth
+    from qwen36_moe_16gb_b200.block import MoEBlock
+
+    shape = synth.QWEN36
+    layer = synth.make_layer(3, 8, shape, with_banks=False)
+    d = {k: v.cuda() for k, v in layer.items()}
+    blk = MoEBlock(d["router_w"], d["shared_gate_up"], d["shared_down"], d["shared_gate"], shape.top_k)
+    x = d["x"]
+    prefill = blk.router_logits(x).float()
+    ws = ops.decode_block_workspace(8, shape.top_k, shape.hidden, shape.intermediate, shape.shared_intermediate, x.device)
+    decode = ops.decode_dense_rows(x, blk.dense, 1, ws).float()
+    exact = x.float() @ d["router_w"].float().t()
+    step = 2.0 ** -8 * exact.abs() * 1.02 + 1e-6   # half a bf16 step of the value, plus the fp32 summation error
+    assert ((prefill - exact).abs() <= step).all() and ((decode - exact).abs() <= step).all()
+    same = (prefill == decode).float().mean().item()
+    assert same > 0.9, same
+    assert ((prefill - decode).abs() <= 2 * step).all()
+    top_p, top_d = prefill.topk(9, dim=1), decode.topk(9, dim=1)
+    for t in range(8):
+        if (top_p.values[t, 7] - top_p.values[t, 8]) > 2 * step[t].max():
+            assert set(top_p.indices[t, :8].tolist()) == set(top_d.indices[t, :8].tolist())

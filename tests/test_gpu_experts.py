@@ -317,14 +317,14 @@ def test_prefill_with_the_shared_expert_on_a_side_stream_is_bit_identical():
     serial = [blk.prefill(x, banks, overlap=False, check_status=True).clone() for x in xs]
     for _ in range(3):
         for x, want in zip(xs, serial):
-            got = blk.prefill(x, banks, check_status=True)
+            got = blk.prefill(x, banks, overlap=True, check_status=True)
             assert torch.equal(got.view(torch.int16), want.view(torch.int16))
     x_buf, out = xs[0].clone(), torch.empty_like(xs[0])
-    blk.prefill(x_buf, banks, out=out)
+    blk.prefill(x_buf, banks, out=out, overlap=True)
     torch.cuda.synchronize()
     graph = torch.cuda.CUDAGraph()
     with torch.cuda.graph(graph):
-        blk.prefill(x_buf, banks, out=out)
+        blk.prefill(x_buf, banks, out=out, overlap=True)
     for x, want in zip(xs, serial):
         x_buf.copy_(x)
         graph.replay()
