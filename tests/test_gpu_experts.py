@@ -329,3 +329,25 @@ def test_prefill_with_the_shared_expert_on_a_side_stream_is_bit_identical():
         x_buf.copy_(x)
         graph.replay()
         assert torch.equal(out.view(torch.int16), want.view(torch.int16))
+
+
+def test_prefill_graphs_replay_the_eager_result_for_refilled_buffers():
+    from qwen36_moe_16gb_b200.block import PrefillGraphs
+
+    shape = synth.Shape(hidden=1024, intermediate=512, num_experts=16, top_k=4, shared_intermediate=256)
+    layer = synth.make_layer(6, 500, shape, zipf_alpha=1.1)
+    d = {k: v.cuda() for k, v in layer.items()}
+    banks = {r: d[r] for r in synth.ROLES}
+    blk = MoEBlock(d["router_w"], d["shared_gate_up"], d["shared_down"], d["shared_gate"], shape.top_k,
+                   logit_bias=d["logit_bias"])
+    graphs = PrefillGraphs(blk, banks)
+    g = torch.Generator(device="cuda").manual_seed(2)
+    bufs = [(torch.empty_like(d["x"]), torch.empty_like(d["x"])) for _ in range(2)]
+    for i in range(6):
+        x = torch.randn(500, shape.hidden, generator=g, device="cuda").bfloat16()
+        want = blk.prefill(x, banks, check_status=True)
+        xb, ob = bufs[i & 1]
+        xb.copy_(x)
+        got = graphs(xb, ob)
+        assert got is ob and torch.equal(got.view(torch.int16), want.view(torch.int16))
+    assert len(graphs.graphs) == 2
