@@ -616,6 +616,9 @@ __global__ void __launch_bounds__(256) gather_rows_f16_kernel(const __nv_bfloat1
   if (src_peers != nullptr) row = src_peers[token / tokens_per_rank] + (int64_t)(token % tokens_per_rank) * lda;
   else row = x + (int64_t)token * lda;
   __half* dst = xs + pos * H;
+  // every token row is read top_k times, far apart in time, while 8 T rows stream out: keep the reads in L2
+  const uint64_t keep = l2_policy_keep(), stream = l2_policy_stream();
+  const bool local = src_peers == nullptr;
   // rows up to 2048 elements stay in registers between the two passes; longer rows are read twice
   uint4 v[8];
   float amax = 0.f;
@@ -624,7 +627,7 @@ __global__ void __launch_bounds__(256) gather_rows_f16_kernel(const __nv_bfloat1
     for (int i = 0; i < 8; ++i) {
       const int k = k0 + (i * 32 + lane) * 8;
       v[i] = make_uint4(0, 0, 0, 0);
-      if (k < H) v[i] = ldg_nc_v4(row + k);
+      if (k < H) v[i] = local ? ldg_nc_v4_policy(row + k, keep) : ldg_nc_v4(row + k);
       const uint32_t w[4] = {v[i].x, v[i].y, v[i].z, v[i].w};
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
@@ -642,7 +645,7 @@ __global__ void __launch_bounds__(256) gather_rows_f16_kernel(const __nv_bfloat1
     for (int i = 0; i < 8; ++i) {
       const int k = k0 + (i * 32 + lane) * 8;
       if (k >= H) continue;
-      if (H > 2048) v[i] = ldg_nc_v4(row + k);
+      if (H > 2048) v[i] = local ? ldg_nc_v4_policy(row + k, keep) : ldg_nc_v4(row + k);
       const uint32_t w[4] = {v[i].x, v[i].y, v[i].z, v[i].w};
       uint32_t o[4];
 #pragma unroll
@@ -650,7 +653,7 @@ __global__ void __launch_bounds__(256) gather_rows_f16_kernel(const __nv_bfloat1
         const __half2 h = __floats2half2_rn(bf16_bits_to_float(w[c] & 0xffffu) * scale, __uint_as_float(w[c] & 0xffff0000u) * scale);
         o[c] = *reinterpret_cast<const uint32_t*>(&h);
       }
-      *reinterpret_cast<uint4*>(dst + k) = make_uint4(o[0], o[1], o[2], o[3]);
+      stg_v4_policy(dst + k, make_uint4(o[0], o[1], o[2], o[3]), stream);
     }
   }
 }

@@ -54,7 +54,7 @@ static int launch_router(const void* logits, int64_t stride, int T, int E, int t
 //   K3 experts : one CTA: padded / unpadded prefix sums, expert_ids, num_tokens_post_pad
 //   K4 scatter : each warp replays its segment in route order -> stable positions
 // ------------------------------------------------------------------------------------------------
-constexpr int SEG = 256;          // routes per warp
+constexpr int SEG = 128;          // routes per warp
 constexpr int PERM_WARPS = 8;     // warps per CTA
 
 __global__ void __launch_bounds__(PERM_WARPS * 32) perm_count_kernel(const int32_t* __restrict__ ids, int numel, int E1,
@@ -71,13 +71,15 @@ __global__ void __launch_bounds__(PERM_WARPS * 32) perm_count_kernel(const int32
   const int seg = blockIdx.x * PERM_WARPS + warp;
   if (seg < nseg) {
     int32_t* mine = sm_counts + warp * E1;
+    int id[SEG / 32];  // all loads of the segment in flight before the first one is used
+#pragma unroll
     for (int it = 0; it < SEG / 32; ++it) {
       const int r = seg * SEG + it * 32 + lane;
-      if (r < numel) {
-        const int id = ids[r];
-        if (id >= 0 && id < E1) atomicAdd(&mine[id], 1);
-      }
+      id[it] = r < numel ? ids[r] : -1;
     }
+#pragma unroll
+    for (int it = 0; it < SEG / 32; ++it)
+      if (id[it] >= 0 && id[it] < E1) atomicAdd(&mine[id[it]], 1);
     __syncwarp();
     for (int e = lane; e < E1; e += 32) seg_counts[(int64_t)seg * E1 + e] = mine[e];
   }
@@ -195,15 +197,20 @@ __global__ void __launch_bounds__(PERM_WARPS * 32) perm_scatter_kernel(const int
   const int seg = blockIdx.x * PERM_WARPS + warp;
   if (seg >= nseg) return;
   int32_t* run = sm_run + warp * E1;
-  for (int e = lane; e < E1; e += 32) run[e] = seg_prefix[(int64_t)seg * E1 + e];
-  __syncwarp();
+  int idr[SEG / 32];  // the segment's ids: loaded together, ahead of the prefix row
+#pragma unroll
   for (int it = 0; it < SEG / 32; ++it) {
     const int r = seg * SEG + it * 32 + lane;
-    int id = -1;
-    if (r < numel) {
-      id = ids[r];
-      if (id < 0 || id >= E1) id = -1;
-    }
+    idr[it] = r < numel ? ids[r] : -1;
+  }
+  // run[e] = routes of expert e in earlier segments; it grows as this segment's routes are placed
+  for (int e = lane; e < E1; e += 32) run[e] = seg_prefix[(int64_t)seg * E1 + e];
+  __syncwarp();
+#pragma unroll
+  for (int it = 0; it < SEG / 32; ++it) {
+    const int r = seg * SEG + it * 32 + lane;
+    int id = idr[it];
+    if (id < 0 || id >= E1) id = -1;
     const unsigned key = id >= 0 ? (unsigned)id : 0x40000000u + lane;  // invalid routes never match
     const unsigned peers = __match_any_sync(0xffffffffu, key);
     int rank = 0;
