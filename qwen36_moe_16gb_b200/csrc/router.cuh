@@ -1,5 +1,7 @@
 // Router selection shared by the stand-alone router kernel and the decode kernels that route in their prologue.
 #pragma once
+#include <type_traits>
+
 #include "common.cuh"
 
 namespace b200moe {
@@ -36,23 +38,49 @@ B200MOE_DEVICE void router_select(const LogitT* __restrict__ src, int E, int top
   float my_w = 0.f;  // lane k keeps the k-th selection of the current group of 32
   int my_id = 0;
   float wsum = 0.f;
-  for (int k = 0; k < top_k; ++k) {
-    float bv = cur[0];
-    int bi = lane;
+  // bf16 logits: (value, id) fits one 32-bit key whose integer order is the selection order -- value rank in the
+  // high bits (twice the order-preserving code of the bf16 bits; NaN takes the odd rank between the two bf16 values
+  // around -1e30), 511 - id below it (lowest id wins among equals); a round is a few integer max and one warp
+  // reduction instead of compare-and-select chains on (float, int) pairs.  Keys of taken or absent experts are 0.
+  constexpr bool KEYED = std::is_same<LogitT, __nv_bfloat16>::value && NPL <= 16;
+  uint32_t key[NPL];
+  if constexpr (KEYED) {
 #pragma unroll
-    for (int i = 1; i < NPL; ++i) {
-      if (cur[i] > bv) {  // strict: the first (lowest id) of equal values stays
-        bv = cur[i];
-        bi = lane + 32 * i;
-      }
+    for (int i = 0; i < NPL; ++i) {
+      const int e = lane + 32 * i;
+      uint32_t b = e < E ? (uint32_t)__bfloat16_as_ushort(src[e]) : 0xff80u;
+      const bool nan = (b & 0x7fffu) > 0x7f80u;
+      const uint32_t ord = (b & 0x8000u) ? (~b & 0xffffu) : (b | 0x8000u);
+      const uint32_t rank = nan ? 2u * 0x0eb5u + 1u : 2u * ord;  // 0x0eb5: code of 0xf14a, the bf16 just below -1e30
+      key[i] = e < E ? (rank << 9) | (uint32_t)(511 - e) : 0u;
     }
+  }
+  for (int k = 0; k < top_k; ++k) {
+    int bi;
+    if constexpr (KEYED) {
+      uint32_t best = key[0];
 #pragma unroll
-    for (int o = 16; o; o >>= 1) {
-      const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
-      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-      if (ov > bv || (ov == bv && oi < bi)) {
-        bv = ov;
-        bi = oi;
+      for (int i = 1; i < NPL; ++i) best = max(best, key[i]);
+      best = __reduce_max_sync(0xffffffffu, best);
+      bi = 511 - (int)(best & 511u);
+    } else {
+      float bv = cur[0];
+      bi = lane;
+#pragma unroll
+      for (int i = 1; i < NPL; ++i) {
+        if (cur[i] > bv) {  // strict: the first (lowest id) of equal values stays
+          bv = cur[i];
+          bi = lane + 32 * i;
+        }
+      }
+#pragma unroll
+      for (int o = 16; o; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (ov > bv || (ov == bv && oi < bi)) {
+          bv = ov;
+          bi = oi;
+        }
       }
     }
     float p = 0.f;
@@ -61,6 +89,7 @@ B200MOE_DEVICE void router_select(const LogitT* __restrict__ src, int E, int top
       if (lane + 32 * i == bi) {
         p = prob[i];
         cur[i] = -INFINITY;
+        key[i] = 0u;
       }
     }
     p = __shfl_sync(0xffffffffu, p, bi & 31);
