@@ -51,8 +51,8 @@ constexpr int WROWS = 128;                           // weight rows a CTA unpack
 constexpr int ITEM_N = 2 * WROWS;                    // weight rows per item (the MMA's N)
 constexpr int TN = 2 * TOK_ROWS;                     // tokens per full tile
 constexpr int A_BYTES = TOK_ROWS * BK * 2, B_BYTES = WROWS * BK * 2;
-constexpr int UNPACK_WARPS = 16, GROUPS = 4, GROUP_WARPS = UNPACK_WARPS / GROUPS;
-constexpr int SUPER = GROUPS;                        // k-steps per staged weight block: 128 packed bytes of every row
+constexpr int GROUP_WARPS = 4;                       // an unpack group: one thread per weight row of a k-step
+constexpr int SUPER = 4;                             // k-steps per staged weight block: 128 packed bytes of every row
 constexpr int W_PACKED_BYTES = WROWS * (SUPER * BK / 2), W_SCALE_BYTES = WROWS * (SUPER * BK / 16);
 constexpr int W_BYTES = W_PACKED_BYTES + W_SCALE_BYTES;
 // Ring depths.  One slot per k-step holds the token rows and the unpacked weight rows (one tcgen05.commit frees
@@ -63,24 +63,20 @@ constexpr int TMEM_COLS = 512;
 static_assert(GROUP_WARPS * 32 == WROWS, "one unpack thread per weight row of a k-step");
 static_assert(W_PACKED_BYTES % 1024 == 0 && W_BYTES % 1024 == 0, "swizzled tiles start on 1024-byte boundaries");
 
-// Warp roles by mode (0 = gate_up + SwiGLU, 1 = down x router weight).  The down GEMM has a quarter of the k-steps
-// per item and twice the output bytes, so it gets eight epilogue warps.
+// Warp roles by mode (0 = gate_up + SwiGLU, 1 = down x router weight).  gate_up has 32 k-steps per item and half an
+// output per weight row: four unpack groups (group g owns the k-steps with index = g mod 4) keep the MMA fed and
+// four epilogue warps drain it.  The down GEMM has eight k-steps per item and 128 KB of output per item: what the
+// MMA waits for is the epilogue, a latency chain per warp (TMEM load, convert, quad exchange, store), so it gets
+// sixteen epilogue warps (four per TMEM lane quarter, 64 columns each) and two unpack groups.
 template <int MODE>
 struct Roles {
-  static constexpr int EPI = MODE == 0 ? 4 : 8;
+  static constexpr int EPI = MODE == 0 ? 4 : 16;
+  static constexpr int GROUPS = MODE == 0 ? 4 : 2;
+  static constexpr int UNPACK_WARPS = GROUPS * GROUP_WARPS;
   static constexpr int UNPACK0 = EPI, TMA_A = EPI + UNPACK_WARPS, TMA_W = TMA_A + 1, RELAY = TMA_W + 1, MMA = RELAY + 1;
   static constexpr int THREADS = (MMA + 1) * 32;
-  // Registers per thread after the roles have traded them (setmaxnreg; roles are whole warpgroups of four warps):
-  // the kernel starts with 65536 / THREADS rounded down to a multiple of 8, the unpack and the single-thread roles
-  // give registers back, the epilogue warps take them.
-  static constexpr int REGS_EPI = MODE == 0 ? 168 : 104, REGS_UNPACK = MODE == 0 ? 72 : 64, REGS_MISC = MODE == 0 ? 56 : 48;
-  static_assert(EPI % 4 == 0 && UNPACK_WARPS % 4 == 0 && MMA + 1 - TMA_A == 4, "roles are whole warpgroups");
-  static_assert(EPI * 32 * REGS_EPI + UNPACK_WARPS * 32 * REGS_UNPACK + 128 * REGS_MISC <= 65536, "register file");
+  static_assert(SUPER % GROUPS == 0, "a group visits every staged block the same number of times");
 };
-template <int N>
-B200MOE_DEVICE void regs_take() {  }
-template <int N>
-B200MOE_DEVICE void regs_give() {  }
 
 struct GgParams {
   CUtensorMap a_map;             // token rows [positions, K] fp16 as 64-column x 64-row boxes, 128B swizzle
@@ -151,7 +147,7 @@ __global__ void __launch_bounds__(Roles<MODE>::THREADS, 1) grouped_gemm_kernel(c
     }
     for (int s = 0; s < SW; ++s) {
       mbar_init(smem_u32(&sh->full_w[s]), 1);            // the weight TMA thread's byte-count arrive (+ bytes)
-      mbar_init(smem_u32(&sh->empty_w[s]), UNPACK_WARPS);  // every unpack warp has read its part of the block
+      mbar_init(smem_u32(&sh->empty_w[s]), R::UNPACK_WARPS * (SUPER / R::GROUPS));  // one arrival per unpack warp and visit
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(smem_u32(&sh->table[b]), EPI_WARPS * 32);
@@ -186,7 +182,6 @@ __global__ void __launch_bounds__(Roles<MODE>::THREADS, 1) grouped_gemm_kernel(c
 
   if (warp < EPI_WARPS) {
     // ------------------------------------------------------------------ epilogue
-    regs_take<R::REGS_EPI>();
     // warp w: TMEM lanes 32 (w % 4) .. +31 (the lanes a warp may touch); with eight warps, w / 4 picks the column half
     const int q = warp & 3, hsel = warp >> 2, jq = lane & 3;
     constexpr int CH = EPI_WARPS / 4;
@@ -200,10 +195,13 @@ __global__ void __launch_bounds__(Roles<MODE>::THREADS, 1) grouped_gemm_kernel(c
       // full form: lane = token rank*128 + lane, columns = weight rows; half form: lanes 0..63 hold tokens
       // rank*64 + lane with weight rows 0..127, lanes 64..127 the same tokens with weight rows 128..255
       const int tok = half ? rank * 64 + (q & 1) * 32 + lane : rank * TOK_ROWS + q * 32 + lane;
-      const int ncols = (half ? ITEM_N / 2 : ITEM_N) / CH;   // TMEM columns of this warp
+      // the warps of a lane quarter split the columns in pieces of at least 64 (the unit of the quad exchange below):
+      // a half-form tile has 128 columns per lane, which keeps two of them busy
+      const int ch = (half && CH > 2) ? 2 : CH;
+      const int ncols = hsel < ch ? (half ? ITEM_N / 2 : ITEM_N) / ch : 0;   // TMEM columns of this warp
       const int col0 = hsel * ncols;
       const int n_base = col0 + (half ? (q >> 1) * (ITEM_N / 2) : 0);  // item column behind TMEM column col0
-      const bool valid = tok < rows;
+      const bool valid = tok < rows && ncols > 0;
       const int pos = info.y + (valid ? tok : 0);
       // the item's per-column globals -> shared memory (one pass of the epilogue threads), then a (bounded) barrier
       // among the epilogue threads: a table is rewritten two items later, after every warp has passed the next one
@@ -303,7 +301,7 @@ __global__ void __launch_bounds__(Roles<MODE>::THREADS, 1) grouped_gemm_kernel(c
     if (tid == 0) { PROF_OUT(0, 3) }
   } else if (warp < R::TMA_A) {
     // ------------------------------------------------------------------ weight unpackers
-    regs_give<R::REGS_UNPACK>();
+    constexpr int GROUPS = R::GROUPS;
     // thread -> weight row `l` of this CTA's half of the item, all 64 k of a k-step: 32 packed bytes, four block scales
     const int u = warp - R::UNPACK0, grp = u / GROUP_WARPS, l = (u % GROUP_WARPS) * 32 + lane;
     const int j = rank * WROWS + l;  // row inside the item
@@ -340,13 +338,13 @@ __global__ void __launch_bounds__(Roles<MODE>::THREADS, 1) grouped_gemm_kernel(c
     };
     if (p.w_staged) {
       // The packed bytes of four k-steps of every row sit in a staged block: rows in box order (gate_up: 64 gate
-      // rows, then 64 up rows), 128 bytes each, 16-byte chunks swizzled by the row; this group's k-step is chunk
-      // pair (2 grp, 2 grp + 1).  Scales: 16 bytes per row after the packed part, four per k-step.
+      // rows, then 64 up rows), 128 bytes each, 16-byte chunks swizzled by the row; k-step kk of the block is chunk
+      // pair (2 kk, 2 kk + 1).  Scales: 16 bytes per row after the packed part, four per k-step.
       const int tr = MODE == 0 ? ((l & 1) ? 64 + (l >> 1) : (l >> 1)) : l;
-      const uint32_t w_off0 = tr * 128 + (((2 * grp) ^ (tr & 7)) << 4), w_off1 = tr * 128 + (((2 * grp + 1) ^ (tr & 7)) << 4);
-      const uint32_t s_off = W_PACKED_BYTES + tr * 16 + grp * 4;
       for (uint32_t it = grp; it < total_steps; it += GROUPS) {
-        const uint32_t blk = it / SUPER;
+        const uint32_t blk = it / SUPER, kk = it % SUPER;   // k-step kk of the block: chunk pair (2 kk, 2 kk + 1)
+        const uint32_t w_off0 = tr * 128 + (((2 * kk) ^ (tr & 7)) << 4), w_off1 = tr * 128 + (((2 * kk + 1) ^ (tr & 7)) << 4);
+        const uint32_t s_off = W_PACKED_BYTES + tr * 16 + kk * 4;
         const int ws = blk % SW;
         PROF_T(w0)
         if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&sh->full_w[ws]), (blk / SW) & 1, abort_flag))) break;
@@ -412,7 +410,6 @@ __global__ void __launch_bounds__(Roles<MODE>::THREADS, 1) grouped_gemm_kernel(c
       }
     }
   } else {
-   regs_give<R::REGS_MISC>();  // the four single-thread roles form one warpgroup
    if (warp == R::TMA_A) {
     // ------------------------------------------------------------------ token rows (A operand)
     if (lane == 0) {
