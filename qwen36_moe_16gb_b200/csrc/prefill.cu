@@ -187,7 +187,7 @@ __global__ void __launch_bounds__(Roles<MODE>::THREADS, 1) grouped_gemm_kernel(c
     constexpr int CH = EPI_WARPS / 4;
     constexpr int NR = MODE == 0 ? 4 : 8;   // registers of one 16-column chunk after conversion (8 fp16 / 16 bf16)
     int tl = 0;
-    PROF_DECL(3)
+    PROF_DECL(6)
     for (int item = unit; item < total_items; item += units, ++tl) {
       const int tt = item / NT, wt = item - tt * NT;
       const int4 info = p.mtiles[tt];
@@ -273,13 +273,17 @@ __global__ void __launch_bounds__(Roles<MODE>::THREADS, 1) grouped_gemm_kernel(c
       for (int c = 0; c < ncols; c += 64) {
         uint32_t blk[4][NR];
         uint32_t v[16];
+        PROF_T(g0)
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
           tc_ld16(tbase + c + 16 * i, v);
           tc_wait_ld();
           convert(v, c + 16 * i, blk[i]);
         }
+        PROF_T(g1)
         quad_transpose<NR>(blk, jq);
+        PROF_T(g2)
+        PROF_ADD(3, g0, g1) PROF_ADD(4, g1, g2)
         // bytes of 64 columns per token: 64 (mode 0, fp16 outputs of 32 pairs) or 128 (mode 1)
         const int gbyte = MODE == 0 ? c : 2 * c;
 #pragma unroll
@@ -287,18 +291,23 @@ __global__ void __launch_bounds__(Roles<MODE>::THREADS, 1) grouped_gemm_kernel(c
           // destination of token k of this lane's quad
           char* dk = reinterpret_cast<char*>(__shfl_sync(0xffffffffu, (unsigned long long)(uintptr_t)dst, (lane & ~3) + k));
           if (dk == nullptr) continue;
+          // lane j of the quad writes piece j of token k: 16 (mode 0) or 32 (mode 1) contiguous bytes, whole sectors
           char* d = dk + gbyte + jq * (NR * 4);
-          stg_v4(d, make_uint4(blk[k][0], blk[k][1], blk[k][2], blk[k][3]));
-          if (NR == 8) stg_v4(d + 16, make_uint4(blk[k][NR - 4], blk[k][NR - 3], blk[k][NR - 2], blk[k][NR - 1]));
+          if constexpr (NR == 8) stg_v8(d, blk[k]);
+          else stg_v4(d, make_uint4(blk[k][0], blk[k][1], blk[k][2], blk[k][3]));
         }
       }
+      PROF_T(e15)
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(leader(&sh->tmem_empty[buf]));
       PROF_T(e2)
-      PROF_ADD(0, e0, e1) PROF_ADD(1, e1, e2) PROF_ADD(2, 0, 1)
+      PROF_ADD(0, e0, e1) PROF_ADD(1, e1, e2) PROF_ADD(2, 0, 1) PROF_ADD(5, e15, e2)
     }
     if (tid == 0) { PROF_OUT(0, 3) }
+#ifdef B200MOE_GG_PROFILE
+    if (tid == 0 && blockIdx.x == 0) for (int i_ = 3; i_ < 6; ++i_) g_gg_prof[MODE][13 + i_] = prof[i_];
+#endif
   } else if (warp < R::TMA_A) {
     // ------------------------------------------------------------------ weight unpackers
     constexpr int GROUPS = R::GROUPS;

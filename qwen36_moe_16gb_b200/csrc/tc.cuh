@@ -146,6 +146,12 @@ B200MOE_DEVICE void sts_v4(uint32_t addr, const uint4& v) {
 B200MOE_DEVICE void stg_v4(void* p, const uint4& v) {
   asm volatile("st.global.v4.b32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
 }
+// 32 contiguous bytes per lane in one instruction (address 32-byte aligned)
+B200MOE_DEVICE void stg_v8(void* p, const uint32_t (&v)[8]) {
+  asm volatile("st.global.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(p), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]),
+               "r"(v[5]), "r"(v[6]), "r"(v[7])
+               : "memory");
+}
 // two floats -> f16x2, values beyond the fp16 range saturate to +-65504
 B200MOE_DEVICE uint32_t pack_f16x2_sat(float lo, float hi) {
   uint32_t r;
