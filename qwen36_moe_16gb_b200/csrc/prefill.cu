@@ -274,11 +274,27 @@ __global__ void __launch_bounds__(Roles<MODE>::THREADS, 1) grouped_gemm_kernel(c
         uint32_t blk[4][NR];
         uint32_t v[16];
         PROF_T(g0)
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          tc_ld16(tbase + c + 16 * i, v);
+        if constexpr (MODE == 0) {
+          // two TMEM loads per wait; the second pair is in flight while the first is converted (the down GEMM's
+          // epilogue has no registers to spare for the second buffer)
+          uint32_t v2[16];
+          tc_ld16(tbase + c, v);
+          tc_ld16(tbase + c + 16, v2);
           tc_wait_ld();
-          convert(v, c + 16 * i, blk[i]);
+          convert(v, c, blk[0]);
+          tc_ld16(tbase + c + 32, v);
+          convert(v2, c + 16, blk[1]);
+          tc_ld16(tbase + c + 48, v2);
+          tc_wait_ld();
+          convert(v, c + 32, blk[2]);
+          convert(v2, c + 48, blk[3]);
+        } else {
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            tc_ld16(tbase + c + 16 * i, v);
+            tc_wait_ld();
+            convert(v, c + 16 * i, blk[i]);
+          }
         }
         PROF_T(g1)
         quad_transpose<NR>(blk, jq);
