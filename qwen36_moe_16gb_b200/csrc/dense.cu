@@ -93,6 +93,7 @@ __global__ void __launch_bounds__(DENSE_THREADS, 1) dense_gemm_kernel(const __gr
     constexpr int PIECE = GROUP / 4;                           // 16 or 8 columns
     constexpr int NR = PIECE / 2;                              // registers of a piece
     int tl = 0;
+    const bool wide_rows = (p.ldo & 15) == 0;   // every row starts on a 32-byte boundary
     for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x, ++tl) {
       const int mt = tile / n_tiles, nt = tile - mt * n_tiles;
       const int buf = tl & 1;
@@ -135,6 +136,12 @@ __global__ void __launch_bounds__(DENSE_THREADS, 1) dense_gemm_kernel(const __gr
           const int col = col_out0 + c + PIECE * jq;
           if (dk == nullptr) continue;
           char* d = dk + (c + PIECE * jq) * 2;
+          if constexpr (NR == 8) {
+            if (wide_rows && col + 16 <= out_cols) {   // 32 contiguous bytes per lane, whole sectors
+              stg_v8(d, blk[k]);
+              continue;
+            }
+          }
 #pragma unroll
           for (int h = 0; h < NR / 4; ++h)
             if (col + 8 * (h + 1) <= out_cols) stg_v4(d + 16 * h, make_uint4(blk[k][4 * h], blk[k][4 * h + 1], blk[k][4 * h + 2], blk[k][4 * h + 3]));
