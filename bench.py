@@ -468,6 +468,7 @@ def run_ours(args) -> None:
     ep_extra = {}
     if world > 1:
         ep_extra = ep_checks(torch, dist, runner, rank)
+        ep_extra["phases_ms_rank0"] = runner.phases_ms()   # every rank runs it (the step has two ring-wide barriers)
         if not args.no_balanced:
             # the same step with the experts dealt by route count instead of contiguous blocks (a deployment
             # choice, reported beside the stated workload)

@@ -126,6 +126,7 @@ class PeerCombine:
         self.x_stage = torch.empty((self.world, tokens, hidden), dtype=torch.bfloat16, device=device)
         self.meta_stage = torch.empty((self.world, tokens, 2 * top_k), dtype=torch.float32, device=device)
         self.events = [torch.cuda.Event() for _ in range(self.world)]
+        self.tokens_published = False
 
     def peer_x(self, r):
         return self.handle.get_buffer(r, (self.tokens, self.hidden), torch.bfloat16, self._offsets[1] // 2)
@@ -135,6 +136,20 @@ class PeerCombine:
 
     def barrier(self):
         self.handle.barrier()  # on the current stream: all ranks' earlier stores are visible afterwards
+
+    def publish_tokens(self, x: torch.Tensor) -> None:
+        """Early half of the exchange: the tokens do not depend on the routing, so a rank can publish them and start
+        pulling the other ranks' tokens (copy stream, ring order) BEFORE it runs its router and shared expert; the
+        pulls then hide behind those GEMMs.  :func:`ep_prefill_step_peer` notices and only exchanges the routing."""
+        main = torch.cuda.current_stream(x.device)
+        self.x.copy_(x)
+        self.barrier()
+        self.x_stage[0].copy_(self.x)
+        self.copy_stream.wait_stream(main)
+        with torch.cuda.stream(self.copy_stream):
+            for j in range(1, self.world):
+                self.x_stage[j].copy_(self.peer_x((self.rank + j) % self.world), non_blocking=True)
+        self.tokens_published = True
 
 
 def source_groups(world: int, sizes) -> list[list[int]]:
@@ -192,7 +207,7 @@ def balanced_placement(counts, world: int, max_per_rank: int | None = None):
 
 
 def ep_prefill_step_peer(dist, peer: PeerCombine, x, topk_weights, topk_ids, num_experts, local_banks, shared=None,
-                         gate=None, placement=None, out=None):
+                         gate=None, placement=None, out=None, marks: list | None = None):
     """Expert-parallel pass with both exchanges off the critical path (GPU only).
 
     Every rank publishes its tokens and routing in symmetric memory; after a barrier it (a) runs the local grouped
@@ -202,28 +217,44 @@ def ep_prefill_step_peer(dist, peer: PeerCombine, x, topk_weights, topk_ids, num
     over routes.
 
     ``placement``: optional ``(owner, local)`` int32 device tensors from :func:`balanced_placement`; without it rank
-    r owns the contiguous experts [r * E / world, (r + 1) * E / world)."""
+    r owns the contiguous experts [r * E / world, (r + 1) * E / world).
+
+    ``marks``: a list that receives ``(phase name, timing event)`` pairs recorded on the current stream at the phase
+    boundaries (diagnostics: the events cost a few microseconds)."""
     from . import ops
 
+    def mark(name):
+        if marks is not None:
+            ev = torch.cuda.Event(enable_timing=True)
+            ev.record(torch.cuda.current_stream(x.device))
+            marks.append((name, ev))
+
+    mark("start")
     world, rank = peer.world, peer.rank
     t, k = topk_ids.shape
     h = x.shape[1]
     epr = num_experts // world
     lo = rank * epr
     main = torch.cuda.current_stream(x.device)
-    peer.x.copy_(x)
+    early = peer.tokens_published                    # publish_tokens(x) ran before the router: the pulls are under way
+    peer.tokens_published = False
+    if not early:
+        peer.x.copy_(x)
     peer.meta.copy_(torch.cat([topk_ids.view(torch.float32), topk_weights], dim=1))
-    peer.barrier()                                   # everyone's tokens and routing are published
+    peer.barrier()                                   # everyone's routing (and tokens) are published
+    mark("publish_and_barrier")
     # staging buffers in ring order: slot j holds the tokens of rank (rank + j) % world; slot 0 is a local copy
-    peer.x_stage[0].copy_(peer.x)
+    if not early:
+        peer.x_stage[0].copy_(peer.x)
     peer.meta_stage[0].copy_(peer.meta)
     peer.copy_stream.wait_stream(main)
     with torch.cuda.stream(peer.copy_stream):
         for j in range(1, world):
             s = (rank + j) % world
-            peer.x_stage[j].copy_(peer.peer_x(s), non_blocking=True)
+            if not early:
+                peer.x_stage[j].copy_(peer.peer_x(s), non_blocking=True)
             peer.meta_stage[j].copy_(peer.peer_meta(s), non_blocking=True)
-            peer.events[j].record(peer.copy_stream)
+            peer.events[j].record(peer.copy_stream)  # the copy stream is in order: the token pulls are covered too
 
     lut = None
     if placement is not None:  # expert id -> row in this rank's banks, or -1; cached on the peer object
@@ -248,11 +279,15 @@ def ep_prefill_step_peer(dist, peer: PeerCombine, x, topk_weights, topk_ids, num
     for grp in source_groups(world, default_group_size(world)):
         if grp[-1] > 0:
             main.wait_event(peer.events[grp[-1]])    # pulls were issued in ring order: the last one covers the chunk
+            mark("wait_tokens_of_ring_%d_%d" % (grp[0], grp[-1]))
         a, b = grp[0], grp[-1] + 1
         st = run(peer.x_stage[a:b].view(-1, h), peer.meta_stage[a:b].view(-1, 2 * k), ((rank + a) % world) * t)
+        mark("grouped_gemms_ring_%d_%d" % (grp[0], grp[-1]))
         status = st if status is None else status
     peer.barrier()                                   # all rows have landed; all peers are done reading my tokens
+    mark("barrier_rows_landed")
     out = ops.combine_routes(peer.ic3.view(t, k, h), topk_ids, num_experts, shared, gate, out=out)
+    mark("combine")
     return out, status
 
 
@@ -262,6 +297,8 @@ class EpPrefill:
     # dense GEMM 3 (router, shared gate_up + SwiGLU, shared down), gate logit 1, router top-k 1, permutation 4,
     # tile list 1, grouped GEMM 2, combine 1 (the token gather between ranks is extra and depends on the ring)
     launches_per_step = 13
+
+    early_tokens = True   # publish the tokens and start the pulls before the router and the shared expert run
 
     def __init__(self, dist, shape, block, banks, x, top_k):
         self.dist, self.shape, self.block, self.banks, self.x, self.top_k = dist, shape, block, banks, x, top_k
@@ -339,19 +376,35 @@ class EpPrefill:
             full[role] = stacked[self.owner.long(), self.local.long()].contiguous()
         return full
 
-    def _run(self, x, out=None):
+    def _run(self, x, out=None, marks=None):
         from . import ops
 
+        if marks is not None:
+            ev = torch.cuda.Event(enable_timing=True)
+            ev.record()
+            marks.append(("begin", ev))
+        if self.early_tokens:
+            self.peer.publish_tokens(x)
         logits = self.block.router_logits(x)
         shared, gate = self.block.shared_parts(x)
         w, ids = ops.fused_topk(x, logits, self.top_k, True)
         out, self.last_status = ep_prefill_step_peer(self.dist, self.peer, x, w, ids, self.shape.num_experts, self.banks,
-                                                     shared, gate, placement=self.placement, out=out)
+                                                     shared, gate, placement=self.placement, out=out, marks=marks)
         self.last_routing = (w, ids)
         return out
 
     def step(self):
         return self._run(self.x)
+
+    def phases_ms(self) -> dict:
+        """One more step with timing events at the phase boundaries: milliseconds per phase on this rank's compute
+        stream (``dense_and_router`` = router logits, shared expert, top-k; the token pulls run on the copy stream and
+        show up only as ``wait_tokens_*``)."""
+        marks: list = []
+        self._run(self.x, marks=marks)
+        torch.cuda.synchronize()
+        names = {"start": "dense_and_router"}
+        return {names.get(n1, n1): round(e0.elapsed_time(e1), 4) for (_, e0), (n1, e1) in zip(marks, marks[1:])}
 
     def e2e_step(self):
         self.x_stage.copy_(self.x_host, non_blocking=True)

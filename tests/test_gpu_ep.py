@@ -54,7 +54,13 @@ def _worker(rank, world, port, ret, group=None):
                                                 ids[sl].contiguous(), shape.num_experts, dealt, placement=(owner, local_idx))
         torch.cuda.synchronize()
         ok_placed = int(status3[0]) == 0 and bool(torch.equal(out3.view(torch.int16), want[sl].view(torch.int16)))
-        ret[rank] = ok_a2a and ok_peer and ok_placed
+        # tokens published (and the pulls started) ahead of the routing exchange
+        peer.publish_tokens(d["x"][sl].contiguous())
+        out4, status4 = ep.ep_prefill_step_peer(dist, peer, d["x"][sl].contiguous(), w[sl].contiguous(),
+                                                ids[sl].contiguous(), shape.num_experts, local)
+        torch.cuda.synchronize()
+        ok_early = int(status4[0]) == 0 and bool(torch.equal(out4.view(torch.int16), want[sl].view(torch.int16)))
+        ret[rank] = ok_a2a and ok_peer and ok_placed and ok_early
     finally:
         dist.destroy_process_group()
 
