@@ -158,4 +158,10 @@ B200MOE_DEVICE float warp_sum(float v) {
   return v;
 }
 
+// b200moe_permute with one more output: inv_routes[route] = sorted position of the route (or -1); may be null.
+int permute_with_inverse(const int32_t* topk_ids, int numel, int num_experts, int block, int32_t* sorted_token_ids,
+                         int sorted_cap, int32_t* expert_ids, int expert_ids_cap, int32_t* num_tokens_post_pad,
+                         int32_t* sorted_routes, int32_t* expert_offsets, int32_t* inv_routes, void* workspace,
+                         int64_t workspace_bytes, void* stream);
+
 }  // namespace b200moe

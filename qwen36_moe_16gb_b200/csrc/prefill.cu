@@ -680,6 +680,60 @@ __global__ void __launch_bounds__(256) gather_rows_f16_kernel(const __nv_bfloat1
   }
 }
 
+// The same copy written the other way round: one warp per TOKEN reads the row once, scales and converts it in
+// registers and writes it to the sorted position of each of its routes (inv_routes: route -> position, -1 = no expert
+// here).  Reads T rows instead of top_k x T; the writes are the same.  Rows of up to 2048 elements.
+__global__ void __launch_bounds__(256) scatter_rows_f16_kernel(const __nv_bfloat16* __restrict__ x, int64_t lda, int T,
+                                                               const int32_t* __restrict__ inv_routes, int top_k, int H,
+                                                               __half* __restrict__ xs, float* __restrict__ inv_out) {
+  const int lane = threadIdx.x & 31;
+  const int64_t t = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  if (t >= T) return;
+  int my_pos = lane < top_k ? inv_routes[t * top_k + lane] : -1;   // lane k holds the position of route k
+  if (__ballot_sync(0xffffffffu, my_pos >= 0) == 0u) return;         // none of the token's experts lives here
+  const __nv_bfloat16* row = x + t * lda;
+  const uint64_t stream = l2_policy_stream();
+  uint4 v[8];
+  float amax = 0.f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int k = (i * 32 + lane) * 8;
+    v[i] = make_uint4(0, 0, 0, 0);
+    if (k < H) v[i] = ldg_nc_v4(row + k);
+    const uint32_t w[4] = {v[i].x, v[i].y, v[i].z, v[i].w};
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      amax = fmaxf(amax, fabsf(bf16_bits_to_float(w[c] & 0xffffu)));
+      amax = fmaxf(amax, fabsf(__uint_as_float(w[c] & 0xffff0000u)));
+    }
+  }
+  amax = warp_max(amax);
+  float scale, inv;
+  f16_row_scale(amax, scale, inv);
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const uint32_t w[4] = {v[i].x, v[i].y, v[i].z, v[i].w};
+    uint32_t o[4];
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      const __half2 h = __floats2half2_rn(bf16_bits_to_float(w[c] & 0xffffu) * scale, __uint_as_float(w[c] & 0xffff0000u) * scale);
+      o[c] = *reinterpret_cast<const uint32_t*>(&h);
+    }
+    v[i] = make_uint4(o[0], o[1], o[2], o[3]);
+  }
+  for (int kk = 0; kk < top_k; ++kk) {
+    const int pos = __shfl_sync(0xffffffffu, my_pos, kk);
+    if (pos < 0) continue;
+    __half* dst = xs + (int64_t)pos * H;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int k = (i * 32 + lane) * 8;
+      if (k < H) stg_v4_policy(dst + k, v[i], stream);
+    }
+    if (lane == 0) inv_out[pos] = inv;
+  }
+}
+
 // out[t] = bf16(sum_k f32(ic3[t,k])) in k order; optional merge with the shared expert.
 template <int TOPK>
 __global__ void __launch_bounds__(256) combine_kernel(const __nv_bfloat16* __restrict__ ic3,
@@ -785,7 +839,7 @@ __global__ void silu_and_mul_kernel(const __nv_bfloat16* __restrict__ in, __nv_b
 struct PrefillWs {
   void* perm_ws;
   int64_t perm_bytes;
-  int32_t *sorted_routes, *offsets, *num_mtiles;
+  int32_t *sorted_routes, *inv_routes, *offsets, *num_mtiles;
   int4* mtiles;
   __half *xs, *ic2;
   float* a_inv;
@@ -801,6 +855,7 @@ static PrefillWs carve_prefill_ws(void* ws, int T, int top_k, int H, int I, int 
   w.perm_bytes = b200moe_permute_workspace_bytes((int)R, slots);
   w.perm_ws = p + off; off += up(w.perm_bytes);
   w.sorted_routes = reinterpret_cast<int32_t*>(p + off); off += up(R * 4);
+  w.inv_routes = reinterpret_cast<int32_t*>(p + off); off += up(R * 4);
   w.offsets = reinterpret_cast<int32_t*>(p + off); off += up(((int64_t)slots + 2) * 4);
   w.num_mtiles = reinterpret_cast<int32_t*>(p + off); off += up(16);
   w.mtiles = reinterpret_cast<int4*>(p + off); off += up((R / TN + slots + 2) * 16);
@@ -984,13 +1039,20 @@ static int prefill_stages_impl(const void* x, const b200moe_banks* banks, const 
   if (stage_mask & B200MOE_STAGE_PLAN) {
     cudaError_t ce = cudaMemsetAsync(status, 0, 4 * sizeof(int32_t), st);
     if (ce != cudaSuccess) return (int)ce;
-    rc = b200moe_permute(topk_ids, R, S, 1, nullptr, 0, nullptr, 0, nullptr, ws.sorted_routes, ws.offsets, ws.perm_ws,
-                         ws.perm_bytes, stream);
+    // rows that fit a warp's registers are read once per token and written to each route's position; longer rows (or
+    // more routes per token than a warp has lanes) are fetched per sorted position
+    const bool by_token = H <= 2048 && top_k <= 32;
+    rc = permute_with_inverse(topk_ids, R, S, 1, nullptr, 0, nullptr, 0, nullptr, ws.sorted_routes, ws.offsets,
+                              by_token ? ws.inv_routes : nullptr, ws.perm_ws, ws.perm_bytes, stream);
     if (rc) return rc;
     build_ttiles_kernel<<<1, 1024, 0, st>>>(ws.offsets, S, ws.mtiles, ws.num_mtiles);
     if ((rc = check_launch())) return rc;
-    gather_rows_f16_kernel<<<(unsigned)(((int64_t)R * 32 + 255) / 256), 256, 0, st>>>(
-        reinterpret_cast<const __nv_bfloat16*>(x), H, nullptr, 1, ws.sorted_routes, ws.offsets, S, top_k, H, ws.xs, ws.a_inv);
+    if (by_token)
+      scatter_rows_f16_kernel<<<(unsigned)(((int64_t)T * 32 + 255) / 256), 256, 0, st>>>(
+          reinterpret_cast<const __nv_bfloat16*>(x), H, T, ws.inv_routes, top_k, H, ws.xs, ws.a_inv);
+    else
+      gather_rows_f16_kernel<<<(unsigned)(((int64_t)R * 32 + 255) / 256), 256, 0, st>>>(
+          reinterpret_cast<const __nv_bfloat16*>(x), H, nullptr, 1, ws.sorted_routes, ws.offsets, S, top_k, H, ws.xs, ws.a_inv);
     if ((rc = check_launch())) return rc;
   }
 

@@ -191,7 +191,8 @@ __global__ void __launch_bounds__(PERM_WARPS * 32) perm_scatter_kernel(const int
                                                                        const int32_t* __restrict__ padded_off,
                                                                        const int32_t* __restrict__ expert_offsets,
                                                                        int32_t* __restrict__ sorted_token_ids,
-                                                                       int32_t* __restrict__ sorted_routes) {
+                                                                       int32_t* __restrict__ sorted_routes,
+                                                                       int32_t* __restrict__ inv_routes) {
   extern __shared__ int32_t sm_run[];  // [PERM_WARPS][E1] running rank inside the expert
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int seg = blockIdx.x * PERM_WARPS + warp;
@@ -222,6 +223,8 @@ __global__ void __launch_bounds__(PERM_WARPS * 32) perm_scatter_kernel(const int
       if (sorted_token_ids != nullptr) sorted_token_ids[padded_off[id] + rank] = r;
       if (sorted_routes != nullptr) sorted_routes[expert_offsets[id] + rank] = r;
     }
+    // inverse of sorted_routes: route -> sorted position, -1 for a route without a valid expert
+    if (inv_routes != nullptr && r < numel) inv_routes[r] = id >= 0 ? expert_offsets[id] + rank : -1;
   }
 }
 
@@ -249,10 +252,11 @@ extern "C" int64_t b200moe_permute_workspace_bytes(int numel, int num_experts) {
   return (nseg * e1 + e1 + e1 + 1 + 8) * 4;
 }
 
-extern "C" int b200moe_permute(const int32_t* topk_ids, int numel, int num_experts, int block, int32_t* sorted_token_ids,
-                               int sorted_cap, int32_t* expert_ids, int expert_ids_cap, int32_t* num_tokens_post_pad,
-                               int32_t* sorted_routes, int32_t* expert_offsets, void* workspace, int64_t workspace_bytes,
-                               void* stream) {
+namespace b200moe {
+int permute_with_inverse(const int32_t* topk_ids, int numel, int num_experts, int block, int32_t* sorted_token_ids,
+                         int sorted_cap, int32_t* expert_ids, int expert_ids_cap, int32_t* num_tokens_post_pad,
+                         int32_t* sorted_routes, int32_t* expert_offsets, int32_t* inv_routes, void* workspace,
+                         int64_t workspace_bytes, void* stream) {
   if (!expert_offsets || !workspace || (numel > 0 && !topk_ids)) return B200MOE_E_NULL;
   if (numel < 0 || num_experts < 1 || num_experts > 1024 || block < 1) return B200MOE_E_SHAPE;
   if (sorted_token_ids && sorted_cap < 0) return B200MOE_E_SHAPE;
@@ -277,8 +281,18 @@ extern "C" int b200moe_permute(const int32_t* topk_ids, int numel, int num_exper
   if ((rc = check_launch())) return rc;
   if (nseg > 0) {
     perm_scatter_kernel<<<ctas, PERM_WARPS * 32, smem, st>>>(topk_ids, numel, E1, nseg, seg_counts, padded_off,
-                                                            expert_offsets, sorted_token_ids, sorted_routes);
+                                                            expert_offsets, sorted_token_ids, sorted_routes, inv_routes);
     if ((rc = check_launch())) return rc;
   }
   return 0;
+}
+}  // namespace b200moe
+
+extern "C" int b200moe_permute(const int32_t* topk_ids, int numel, int num_experts, int block, int32_t* sorted_token_ids,
+                               int sorted_cap, int32_t* expert_ids, int expert_ids_cap, int32_t* num_tokens_post_pad,
+                               int32_t* sorted_routes, int32_t* expert_offsets, void* workspace, int64_t workspace_bytes,
+                               void* stream) {
+  return b200moe::permute_with_inverse(topk_ids, numel, num_experts, block, sorted_token_ids, sorted_cap, expert_ids,
+                                       expert_ids_cap, num_tokens_post_pad, sorted_routes, expert_offsets, nullptr, workspace,
+                                       workspace_bytes, stream);
 }
