@@ -252,7 +252,10 @@ enum {
   B200MOE_STAGE_GEMM1 = 2,   /* gate_up grouped GEMM + SwiGLU */
   B200MOE_STAGE_GEMM2 = 4,   /* down grouped GEMM * router weight */
   B200MOE_STAGE_COMBINE = 8, /* sum over routes (+ merge) */
-  B200MOE_STAGE_ALL = 15
+  B200MOE_STAGE_ALL = 15,
+  B200MOE_STAGE_ROUTE_ORDER = 16 /* modifier: leave the per-route rows [T, top_k, hidden] in route order in the workspace
+                                    (for a caller that reads them); without it they sit in expert order and only the
+                                    combine stage, given the same modifier state, can use them */
 };
 int b200moe_prefill_stages(const void* x, const b200moe_banks* banks, const float* topk_weights,
                            const int32_t* topk_ids, int T, int top_k, const void* shared,

@@ -51,13 +51,19 @@ constexpr int WROWS = 128;                           // weight rows a CTA unpack
 constexpr int ITEM_N = 2 * WROWS;                    // weight rows per item (the MMA's N)
 constexpr int TN = 2 * TOK_ROWS;                     // tokens per full tile
 constexpr int A_BYTES = TOK_ROWS * BK * 2, B_BYTES = WROWS * BK * 2;
+#ifndef B200MOE_DIRECT_ARRIVE
+#define B200MOE_DIRECT_ARRIVE 1
+#endif
+#ifndef B200MOE_ST1
+#define B200MOE_ST1 4
+#endif
 constexpr int GROUP_WARPS = 4;                       // an unpack group: one thread per weight row of a k-step
 constexpr int SUPER = 4;                             // k-steps per staged weight block: 128 packed bytes of every row
 constexpr int W_PACKED_BYTES = WROWS * (SUPER * BK / 2), W_SCALE_BYTES = WROWS * (SUPER * BK / 16);
 constexpr int W_BYTES = W_PACKED_BYTES + W_SCALE_BYTES;
 // Ring depths.  One slot per k-step holds the token rows and the unpacked weight rows (one tcgen05.commit frees
 // both): five k-steps; staged packed weights: three blocks of four k-steps.
-constexpr int ST = 5, SW = 3;
+constexpr int ST_MAX = 5, SW = 3;
 constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
 constexpr int TMEM_COLS = 512;
 static_assert(GROUP_WARPS * 32 == WROWS, "one unpack thread per weight row of a k-step");
@@ -72,6 +78,7 @@ template <int MODE>
 struct Roles {
   static constexpr int EPI = MODE == 0 ? 4 : 16;
   static constexpr int GROUPS = MODE == 0 ? 4 : 2;
+  static constexpr int ST = MODE == 0 ? 5 : B200MOE_ST1;   // operand ring slots (one k-step each)
   static constexpr int UNPACK_WARPS = GROUPS * GROUP_WARPS;
   static constexpr int UNPACK0 = EPI, TMA_A = EPI + UNPACK_WARPS, TMA_W = TMA_A + 1, RELAY = TMA_W + 1, MMA = RELAY + 1;
   static constexpr int THREADS = (MMA + 1) * 32;
@@ -94,7 +101,9 @@ struct GgParams {
   const int32_t* sorted_routes;  // sorted position -> flat route id
   const float* topk_w;           // [routes]
   const float* a_inv;            // mode 0: inverse of the power-of-two scale of every token row
-  void* out;                     // mode 0: ic2 [pos, half_n] fp16; mode 1: ic3 [route, N] bf16
+  void* out;                     // mode 0: ic2 [pos, half_n] fp16; mode 1: ic3 bf16, [route, N] or [pos, N] (out_sorted)
+  CUtensorMap o_map;             // mode 1, out_sorted: ic3 [pos, N] as 32-column x 32-row boxes, 64B swizzle
+  int out_sorted;                // mode 1: rows go to their sorted position (whole 32-row groups by TMA store)
   __nv_bfloat16* const* out_peers;  // mode 1, expert parallel: ic3 of every rank (peer-mapped), or null
   int routes_per_rank;           // global route g belongs to rank g / routes_per_rank
   int64_t route_offset;          // global route = (local route + route_offset) mod total_routes: a call covers a slice of
@@ -103,13 +112,13 @@ struct GgParams {
 };
 
 struct alignas(16) GgShared {
-  unsigned long long full[ST], empty[ST], part[ST], full_w[SW], empty_w[SW];
+  unsigned long long full[ST_MAX], empty[ST_MAX], part[ST_MAX], full_w[SW], empty_w[SW];
   unsigned long long tmem_full[2], tmem_empty[2], table[2];
   uint32_t tmem_base;
   int abort_flag;
   alignas(16) float gl[2][ITEM_N];  // per accumulator buffer: the fp32 global of every column of the item
 };
-constexpr size_t GG_SMEM = 1024 + (size_t)ST * STAGE_BYTES + (size_t)SW * W_BYTES + sizeof(GgShared);
+constexpr size_t GG_SMEM = 1024 + (size_t)ST_MAX * STAGE_BYTES + (size_t)SW * W_BYTES + sizeof(GgShared);
 
 // Cycle accounting of the roles of CTA 0 (diagnostic build, -DB200MOE_GG_PROFILE): every role adds up the cycles
 // it spends in its waits and in its work; read back with b200moe_debug_gg_profile.
@@ -132,7 +141,8 @@ __global__ void __launch_bounds__(Roles<MODE>::THREADS, 1) grouped_gemm_kernel(c
   constexpr int EPI_WARPS = R::EPI;
   extern __shared__ unsigned char smem_dyn[];
   unsigned char* ring = reinterpret_cast<unsigned char*>(((uintptr_t)smem_dyn + 1023) & ~(uintptr_t)1023);
-  GgShared* sh = reinterpret_cast<GgShared*>(ring + (size_t)ST * STAGE_BYTES + (size_t)SW * W_BYTES);
+  constexpr int ST = R::ST;
+  GgShared* sh = reinterpret_cast<GgShared*>(ring + (size_t)ST_MAX * STAGE_BYTES + (size_t)SW * W_BYTES);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const uint32_t ring_u32 = smem_u32(ring), ring_w = ring_u32 + ST * STAGE_BYTES;
   volatile int* abort_flag = &sh->abort_flag;
@@ -141,7 +151,9 @@ __global__ void __launch_bounds__(Roles<MODE>::THREADS, 1) grouped_gemm_kernel(c
 
   if (tid == 0) {
     for (int s = 0; s < ST; ++s) {
-      mbar_init(smem_u32(&sh->full[s]), 3);              // the leader's byte-count arrive (+ the bytes of both CTAs), one relay per CTA
+      // the leader's byte-count arrive (+ the bytes of both CTAs) and either one relay per CTA or every unpack warp of the
+      // k-step's group in both CTAs
+      mbar_init(smem_u32(&sh->full[s]), B200MOE_DIRECT_ARRIVE ? 1 + 2 * GROUP_WARPS : 3);
       mbar_init(smem_u32(&sh->empty[s]), 1);             // the MMA thread's commit
       mbar_init(smem_u32(&sh->part[s]), GROUP_WARPS);    // this CTA's unpack warps of the k-step's group
     }
@@ -219,7 +231,7 @@ __global__ void __launch_bounds__(Roles<MODE>::THREADS, 1) grouped_gemm_kernel(c
       } else {
         const int route = p.sorted_routes[pos];
         mul = p.topk_w[route];
-        __nv_bfloat16* base = reinterpret_cast<__nv_bfloat16*>(p.out) + (int64_t)route * p.N;
+        __nv_bfloat16* base = reinterpret_cast<__nv_bfloat16*>(p.out) + (int64_t)(p.out_sorted ? pos : route) * p.N;
         if (p.out_peers != nullptr) {  // the row goes straight to the token's home GPU over NVLink
           int64_t groute = route + p.route_offset;
           if (groute >= p.total_routes) groute -= p.total_routes;
@@ -267,6 +279,47 @@ __global__ void __launch_bounds__(Roles<MODE>::THREADS, 1) grouped_gemm_kernel(c
           }
         }
       };
+      // Down GEMM with rows in sorted order: a warp whose 32 tile rows are all real routes owns a 32 x 64 box of
+      // consecutive rows of ic3.  It converts chunk by chunk into its staging tile (row = lane, 16-byte chunks
+      // swizzled by the row like a TMA tile, so the stores hit every bank once) and one lane hands the tile to a TMA
+      // store: no exchange between lanes and no store instructions in the chain.  The staging tile is rewritten only
+      // after the previous store has read it.  (The 32 KB of staging tiles cost this GEMM one of its ring slots.)
+      bool by_tma = false;
+      if constexpr (MODE == 1) by_tma = p.out_sorted && ncols > 0 && tok - lane + 32 <= rows;
+      if (by_tma) {
+        // two halves of 32 columns through one 2 KB staging tile (64-byte rows, 64B swizzle): the first half's store
+        // has long read the tile when the second half is converted
+        const uint32_t stage = ring_u32 + ST * STAGE_BYTES + SW * W_BYTES + warp * 2048;
+        const uint32_t srow = stage + lane * 64, sx = (lane >> 1) & 3;
+        uint32_t v[16];
+#pragma unroll
+        for (int hh = 0; hh < 2; ++hh) {
+#pragma unroll
+          for (int ii = 0; ii < 2; ++ii) {
+            tc_ld16(tbase + 32 * hh + 16 * ii, v);
+            tc_wait_ld();
+            uint32_t o[NR];
+            convert(v, 32 * hh + 16 * ii, o);
+            if (ii == 0) {
+              if (lane == 0) bulk_wait_read_all();
+              __syncwarp();
+            }
+            sts_v4(srow + (((2 * ii) ^ sx) << 4), make_uint4(o[0], o[1], o[2], o[3]));
+            sts_v4(srow + (((2 * ii + 1) ^ sx) << 4), make_uint4(o[NR - 4], o[NR - 3], o[NR - 2], o[NR - 1]));
+          }
+          if (hh == 1) tc_fence_before();
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+          __syncwarp();
+          if (lane == 0) {
+            if (hh == 1) mbar_arrive_cluster(leader(&sh->tmem_empty[buf]));
+            tma_store_2d(&p.o_map, stage, wt * ITEM_N + n_base + 32 * hh, info.y + tok - lane);
+            bulk_commit();
+          }
+        }
+        PROF_T(e2)
+        PROF_ADD(0, e0, e1) PROF_ADD(1, e1, e2) PROF_ADD(2, 0, 1)
+        continue;
+      }
       // 64 columns at a time: four chunks, exchanged inside the quad so that lane j holds piece j of the outputs
       // of each of the quad's four tokens; a store instruction then covers contiguous pieces of eight tokens
 #pragma unroll 1
@@ -320,6 +373,7 @@ __global__ void __launch_bounds__(Roles<MODE>::THREADS, 1) grouped_gemm_kernel(c
       PROF_T(e2)
       PROF_ADD(0, e0, e1) PROF_ADD(1, e1, e2) PROF_ADD(2, 0, 1) PROF_ADD(5, e15, e2)
     }
+    if (MODE == 1 && lane == 0) bulk_wait_all();   // this warp's TMA stores have left shared memory and landed
     if (tid == 0) { PROF_OUT(0, 3) }
 #ifdef B200MOE_GG_PROFILE
     if (tid == 0 && blockIdx.x == 0) for (int i_ = 3; i_ < 6; ++i_) g_gg_prof[MODE][13 + i_] = prof[i_];
@@ -336,6 +390,7 @@ __global__ void __launch_bounds__(Roles<MODE>::THREADS, 1) grouped_gemm_kernel(c
     // BEFORE it waits (the wait -> store -> fence -> relay chain is what the MMA thread waits for); down, with 28
     // warps and 72 registers per thread, unpacks chunk by chunk after the wait.  `release` runs once the packed
     // registers have been consumed (the staged path frees its block there).
+    constexpr bool PRE_UNPACK = MODE == 0;   // the down GEMM's 72 registers per thread do not hold the unpacked row
     auto produce_row = [&](uint32_t it, const uint4& q0, const uint4& q1, uint32_t sc, auto release) -> bool {
       const int s = it % ST;
       const uint32_t s01 = e4m3x2_to_f16x2(sc & 0xffffu), s23 = e4m3x2_to_f16x2(sc >> 16);
@@ -343,7 +398,7 @@ __global__ void __launch_bounds__(Roles<MODE>::THREADS, 1) grouped_gemm_kernel(c
       const uint32_t w[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
       const uint32_t sw[4] = {sc0, sc1, sc2, sc3};
       uint4 c[8];
-      if (MODE == 0) {
+      if (PRE_UNPACK) {
 #pragma unroll
         for (int i = 0; i < 8; ++i) c[i] = unpack_chunk_f16(w[i], sw[i >> 1]);
         release();
@@ -354,11 +409,14 @@ __global__ void __launch_bounds__(Roles<MODE>::THREADS, 1) grouped_gemm_kernel(c
       PROF_ADD(1, u0, u1)
       const uint32_t sb = ring_u32 + s * STAGE_BYTES + A_BYTES + b_row;
 #pragma unroll
-      for (int i = 0; i < 8; ++i) sts_v4(sb + ((i ^ b_x) << 4), MODE == 0 ? c[i] : unpack_chunk_f16(w[i], sw[i >> 1]));
-      if (MODE != 0) release();
+      for (int i = 0; i < 8; ++i) sts_v4(sb + ((i ^ b_x) << 4), PRE_UNPACK ? c[i] : unpack_chunk_f16(w[i], sw[i >> 1]));
+      if (!PRE_UNPACK) release();
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(&sh->part[s]));
+      if (lane == 0) {
+        if (B200MOE_DIRECT_ARRIVE) mbar_arrive_cluster(leader(&sh->full[s]));
+        else mbar_arrive(smem_u32(&sh->part[s]));
+      }
       return true;
     };
     if (p.w_staged) {
@@ -493,7 +551,7 @@ __global__ void __launch_bounds__(Roles<MODE>::THREADS, 1) grouped_gemm_kernel(c
   } else if (warp == R::RELAY) {
     // ------------------------------------------------------------------ relay: this CTA's weight half of a k-step -> leader
     // (no proxy fence here: the unpackers fenced their own stores)
-    if (lane == 0) {
+    if (lane == 0 && !B200MOE_DIRECT_ARRIVE) {
       const uint32_t leader_full = leader(&sh->full[0]);
       for (uint32_t it = 0; it < total_steps; ++it) {
         const int s = it % ST;
@@ -737,6 +795,7 @@ __global__ void __launch_bounds__(256) scatter_rows_f16_kernel(const __nv_bfloat
 // out[t] = bf16(sum_k f32(ic3[t,k])) in k order; optional merge with the shared expert.
 template <int TOPK>
 __global__ void __launch_bounds__(256) combine_kernel(const __nv_bfloat16* __restrict__ ic3,
+                                                      const int32_t* __restrict__ inv,  // route -> row of ic3 (-1: none) or null
                                                       const int32_t* __restrict__ ids, int num_slots, int T,
                                                       int top_k, int H, const __nv_bfloat16* __restrict__ shared,
                                                       const __nv_bfloat16* __restrict__ gate,
@@ -758,11 +817,17 @@ __global__ void __launch_bounds__(256) combine_kernel(const __nv_bfloat16* __res
   };
   if (TOPK > 0) {
     bool live[TOPK > 0 ? TOPK : 1];
+    int64_t row[TOPK > 0 ? TOPK : 1];
     uint4 q[TOPK > 0 ? TOPK : 1];
 #pragma unroll
     for (int k = 0; k < TOPK; ++k) {
       live[k] = true;
-      if (ids != nullptr) {
+      row[k] = (int64_t)t * TOPK + k;
+      if (inv != nullptr) {   // rows in sorted order: the permutation's inverse says where (and whether) a route landed
+        const int pos = inv[(int64_t)t * TOPK + k];
+        live[k] = pos >= 0;
+        row[k] = pos;
+      } else if (ids != nullptr) {
         const int id = ids[(int64_t)t * TOPK + k];
         live[k] = id >= 0 && id < num_slots;  // dropped route: its ic3 row was never written
       }
@@ -770,18 +835,23 @@ __global__ void __launch_bounds__(256) combine_kernel(const __nv_bfloat16* __res
 #pragma unroll
     for (int k = 0; k < TOPK; ++k) {
       q[k] = make_uint4(0, 0, 0, 0);
-      if (live[k]) q[k] = ldg_nc_v4(ic3 + ((int64_t)t * TOPK + k) * H + h);
+      if (live[k]) q[k] = ldg_nc_v4(ic3 + row[k] * H + h);
     }
 #pragma unroll
     for (int k = 0; k < TOPK; ++k)
       if (live[k]) add(q[k]);
   } else {
     for (int k = 0; k < top_k; ++k) {
-      if (ids != nullptr) {
-        const int id = ids[(int64_t)t * top_k + k];
+      int64_t row = (int64_t)t * top_k + k;
+      if (inv != nullptr) {
+        const int pos = inv[row];
+        if (pos < 0) continue;
+        row = pos;
+      } else if (ids != nullptr) {
+        const int id = ids[row];
         if (id < 0 || id >= num_slots) continue;
       }
-      add(*reinterpret_cast<const uint4*>(ic3 + ((int64_t)t * top_k + k) * H + h));
+      add(*reinterpret_cast<const uint4*>(ic3 + row * H + h));
     }
   }
   if (shared != nullptr) {
@@ -799,13 +869,13 @@ __global__ void __launch_bounds__(256) combine_kernel(const __nv_bfloat16* __res
       make_uint4(pack_bf16x2(acc[0], acc[1]), pack_bf16x2(acc[2], acc[3]), pack_bf16x2(acc[4], acc[5]), pack_bf16x2(acc[6], acc[7]));
 }
 
-static int launch_combine(const __nv_bfloat16* ic3, const int32_t* ids, int num_slots, int T, int top_k, int H,
-                          const __nv_bfloat16* shared, const __nv_bfloat16* gate, __nv_bfloat16* out, cudaStream_t st) {
+static int launch_combine(const __nv_bfloat16* ic3, const int32_t* inv, const int32_t* ids, int num_slots, int T, int top_k,
+                          int H, const __nv_bfloat16* shared, const __nv_bfloat16* gate, __nv_bfloat16* out, cudaStream_t st) {
   const int64_t groups = (int64_t)T * (H / 8);
   const unsigned grid = (unsigned)((groups + 255) / 256);
-  if (top_k == 8) combine_kernel<8><<<grid, 256, 0, st>>>(ic3, ids, num_slots, T, top_k, H, shared, gate, out);
-  else if (top_k == 1) combine_kernel<1><<<grid, 256, 0, st>>>(ic3, ids, num_slots, T, top_k, H, shared, gate, out);
-  else combine_kernel<0><<<grid, 256, 0, st>>>(ic3, ids, num_slots, T, top_k, H, shared, gate, out);
+  if (top_k == 8) combine_kernel<8><<<grid, 256, 0, st>>>(ic3, inv, ids, num_slots, T, top_k, H, shared, gate, out);
+  else if (top_k == 1) combine_kernel<1><<<grid, 256, 0, st>>>(ic3, inv, ids, num_slots, T, top_k, H, shared, gate, out);
+  else combine_kernel<0><<<grid, 256, 0, st>>>(ic3, inv, ids, num_slots, T, top_k, H, shared, gate, out);
   return check_launch();
 }
 
@@ -874,7 +944,9 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 static std::mutex g_prefill_lock;
 static EncodeTiledFn g_encode_tiled = nullptr;
-static int encode_rows_map(CUtensorMap* map, const void* base, int64_t rows, int64_t cols, int64_t pitch) {
+static int encode_rows_map(CUtensorMap* map, const void* base, int64_t rows, int64_t cols, int64_t pitch,
+                           int box_rows = 64, CUtensorMapDataType dtype = CU_TENSOR_MAP_DATA_TYPE_FLOAT16, int box_cols = BK,
+                           CUtensorMapSwizzle swizzle = CU_TENSOR_MAP_SWIZZLE_128B) {
   EncodeTiledFn& encode = g_encode_tiled;
   {
     std::lock_guard<std::mutex> guard(g_prefill_lock);
@@ -889,9 +961,9 @@ static int encode_rows_map(CUtensorMap* map, const void* base, int64_t rows, int
   }
   const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
   const cuuint64_t strides[1] = {(cuuint64_t)pitch * 2};
-  const cuuint32_t box[2] = {(cuuint32_t)BK, 64}, elem[2] = {1, 1};
-  const CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
-                            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+  const cuuint32_t box[2] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows}, elem[2] = {1, 1};
+  const CUresult r = encode(map, dtype, 2, const_cast<void*>(base), dims, strides, box, elem,
+                            CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? 0 : B200MOE_E_ALIGN;
 }
@@ -1043,7 +1115,7 @@ static int prefill_stages_impl(const void* x, const b200moe_banks* banks, const 
     // more routes per token than a warp has lanes) are fetched per sorted position
     const bool by_token = H <= 2048 && top_k <= 32;
     rc = permute_with_inverse(topk_ids, R, S, 1, nullptr, 0, nullptr, 0, nullptr, ws.sorted_routes, ws.offsets,
-                              by_token ? ws.inv_routes : nullptr, ws.perm_ws, ws.perm_bytes, stream);
+                              ws.inv_routes, ws.perm_ws, ws.perm_bytes, stream);
     if (rc) return rc;
     build_ttiles_kernel<<<1, 1024, 0, st>>>(ws.offsets, S, ws.mtiles, ws.num_mtiles);
     if ((rc = check_launch())) return rc;
@@ -1109,12 +1181,19 @@ static int prefill_stages_impl(const void* x, const b200moe_banks* banks, const 
   g2.routes_per_rank = routes_per_rank > 0 ? routes_per_rank : 1;
   g2.route_offset = route_offset;
   g2.total_routes = total_routes > 0 ? total_routes : (int64_t)1 << 62;
+  // Per-route rows: in sorted (expert) order when they stay in this workspace for the combine stage -- a tile's rows
+  // are then consecutive and leave by TMA store, and the combine stage finds them through the inverse permutation;
+  // in route order when they go to their home GPUs or when the caller reads them (B200MOE_STAGE_ROUTE_ORDER).
+  const bool sorted_out = out_peers == nullptr && !(stage_mask & B200MOE_STAGE_ROUTE_ORDER);
+  g2.out_sorted = sorted_out;
+  if (sorted_out && (rc = encode_rows_map(&g2.o_map, ws.ic3, R, H, H, 32, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 32, CU_TENSOR_MAP_SWIZZLE_64B))) return rc;
   if (stage_mask & B200MOE_STAGE_GEMM2) {
     rc = launch_grouped_gemm<1>(g2, (int)std::min<int64_t>(pairs, (int64_t)max_mtiles * g2.NT), st);
     if (rc) return rc;
   }
   if (stage_mask & B200MOE_STAGE_COMBINE) {
-    rc = launch_combine(ws.ic3, topk_ids, S, T, top_k, H, reinterpret_cast<const __nv_bfloat16*>(shared),
+    rc = launch_combine(ws.ic3, sorted_out ? ws.inv_routes : nullptr, topk_ids, S, T, top_k, H,
+                        reinterpret_cast<const __nv_bfloat16*>(shared),
                         reinterpret_cast<const __nv_bfloat16*>(shared_gate_logit), reinterpret_cast<__nv_bfloat16*>(out), st);
     if (rc) return rc;
   }
@@ -1174,7 +1253,7 @@ extern "C" int b200moe_shared_epilogue(const void* routed, const void* shared, c
   if (!routed || !shared || !gate || !out) return B200MOE_E_NULL;
   if (T < 0 || H < 8 || H % 8) return B200MOE_E_SHAPE;
   if (!aligned16(routed) || !aligned16(shared) || !aligned16(out)) return B200MOE_E_ALIGN;
-  return launch_combine(reinterpret_cast<const __nv_bfloat16*>(routed), nullptr, 0, T, 1, H,
+  return launch_combine(reinterpret_cast<const __nv_bfloat16*>(routed), nullptr, nullptr, 0, T, 1, H,
                         reinterpret_cast<const __nv_bfloat16*>(shared), reinterpret_cast<const __nv_bfloat16*>(gate),
                         reinterpret_cast<__nv_bfloat16*>(out), reinterpret_cast<cudaStream_t>(stream));
 }
@@ -1184,7 +1263,7 @@ extern "C" int b200moe_sum_routes(const void* in, void* out, int T, int top_k, i
   if (!in || !out) return B200MOE_E_NULL;
   if (T < 0 || top_k < 1 || H < 8 || H % 8) return B200MOE_E_SHAPE;
   if (!aligned16(in) || !aligned16(out)) return B200MOE_E_ALIGN;
-  return launch_combine(reinterpret_cast<const __nv_bfloat16*>(in), nullptr, 0, T, top_k, H, nullptr, nullptr,
+  return launch_combine(reinterpret_cast<const __nv_bfloat16*>(in), nullptr, nullptr, 0, T, top_k, H, nullptr, nullptr,
                         reinterpret_cast<__nv_bfloat16*>(out), reinterpret_cast<cudaStream_t>(stream));
 }
 
@@ -1195,7 +1274,7 @@ extern "C" int b200moe_combine_routes(const void* ic3, const int32_t* topk_ids, 
   if ((shared == nullptr) != (shared_gate_logit == nullptr)) return B200MOE_E_NULL;
   if (T < 0 || top_k < 1 || H < 8 || H % 8) return B200MOE_E_SHAPE;
   if (!aligned16(ic3) || !aligned16(out) || (shared && !aligned16(shared))) return B200MOE_E_ALIGN;
-  return launch_combine(reinterpret_cast<const __nv_bfloat16*>(ic3), topk_ids, num_slots, T, top_k, H,
+  return launch_combine(reinterpret_cast<const __nv_bfloat16*>(ic3), nullptr, topk_ids, num_slots, T, top_k, H,
                         reinterpret_cast<const __nv_bfloat16*>(shared), reinterpret_cast<const __nv_bfloat16*>(shared_gate_logit),
                         reinterpret_cast<__nv_bfloat16*>(out), reinterpret_cast<cudaStream_t>(stream));
 }

@@ -51,6 +51,16 @@ B200MOE_DEVICE void tma_load_3d(uint32_t dst, const CUtensorMap* map, int c0, in
                ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(bar)
                : "memory");
 }
+// One box of this CTA's shared memory -> a 2-D tensor in global memory (bulk async-group completion): commit after
+// issuing, wait for the READ of shared memory before the buffer is rewritten, wait for everything before exit.
+B200MOE_DEVICE void tma_store_2d(const CUtensorMap* map, uint32_t src, int col, int row) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%1, %2}], [%3];"
+               ::"l"(map), "r"(col), "r"(row), "r"(src)
+               : "memory");
+}
+B200MOE_DEVICE void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+B200MOE_DEVICE void bulk_wait_read_all() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+B200MOE_DEVICE void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 B200MOE_DEVICE bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   uint32_t ok;
   asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"

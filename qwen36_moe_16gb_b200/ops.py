@@ -190,7 +190,7 @@ class PrefillStatus(RuntimeError):
     pass
 
 
-STAGE_PLAN, STAGE_GEMM1, STAGE_GEMM2, STAGE_COMBINE, STAGE_ALL = 1, 2, 4, 8, 15
+STAGE_PLAN, STAGE_GEMM1, STAGE_GEMM2, STAGE_COMBINE, STAGE_ALL, STAGE_ROUTE_ORDER = 1, 2, 4, 8, 15, 16
 
 
 def prefill_experts(x, banks: dict[str, torch.Tensor], topk_weights, topk_ids, shared=None, shared_gate_logit=None,
@@ -313,7 +313,7 @@ def prefill_route_rows(x, banks: dict[str, torch.Tensor], topk_weights, topk_ids
     ws = _workspace("prefill", nbytes + 64, x.device)
     status = ws[nbytes:nbytes + 16].view(torch.int32)
     check(lib().b200moe_prefill_stages(ptr(x), C.byref(b), ptr(topk_weights), ptr(topk_ids), t, k, None, None, ptr(x),
-                                       ptr(ws), nbytes, ptr(status), STAGE_PLAN | STAGE_GEMM1 | STAGE_GEMM2,
+                                       ptr(ws), nbytes, ptr(status), STAGE_PLAN | STAGE_GEMM1 | STAGE_GEMM2 | STAGE_ROUTE_ORDER,
                                        stream_ptr()), "b200moe_prefill_stages")
     off = lib().b200moe_prefill_ic3_offset(t, k, h, b.intermediate, b.num_slots)
     return ws[off:off + t * k * h * 2].view(torch.bfloat16).view(t, k, h)
