@@ -103,7 +103,8 @@ struct GgParams {
   const float* a_inv;            // mode 0: inverse of the power-of-two scale of every token row
   void* out;                     // mode 0: ic2 [pos, half_n] fp16; mode 1: ic3 bf16, [route, N] or [pos, N] (out_sorted)
   CUtensorMap o_map;             // mode 1, out_sorted: ic3 [pos, N] as 32-column x 32-row boxes, 64B swizzle
-  int out_sorted;                // mode 1: rows go to their sorted position (whole 32-row groups by TMA store)
+  int out_sorted;                // mode 1: rows go to their sorted position + pad_off[slot], 32-row groups by TMA store
+  const int32_t* pad_off;        // [slots]: shift of a slot's rows in the padded expert order
   __nv_bfloat16* const* out_peers;  // mode 1, expert parallel: ic3 of every rank (peer-mapped), or null
   int routes_per_rank;           // global route g belongs to rank g / routes_per_rank
   int64_t route_offset;          // global route = (local route + route_offset) mod total_routes: a call covers a slice of
@@ -231,7 +232,7 @@ __global__ void __launch_bounds__(Roles<MODE>::THREADS, 1) grouped_gemm_kernel(c
       } else {
         const int route = p.sorted_routes[pos];
         mul = p.topk_w[route];
-        __nv_bfloat16* base = reinterpret_cast<__nv_bfloat16*>(p.out) + (int64_t)(p.out_sorted ? pos : route) * p.N;
+        __nv_bfloat16* base = reinterpret_cast<__nv_bfloat16*>(p.out) + (int64_t)route * p.N;
         if (p.out_peers != nullptr) {  // the row goes straight to the token's home GPU over NVLink
           int64_t groute = route + p.route_offset;
           if (groute >= p.total_routes) groute -= p.total_routes;
@@ -279,18 +280,19 @@ __global__ void __launch_bounds__(Roles<MODE>::THREADS, 1) grouped_gemm_kernel(c
           }
         }
       };
-      // Down GEMM with rows in sorted order: a warp whose 32 tile rows are all real routes owns a 32 x 64 box of
-      // consecutive rows of ic3.  It converts chunk by chunk into its staging tile (row = lane, 16-byte chunks
+      // Down GEMM with rows in (padded) expert order: a warp with at least one real route among its 32 tile rows owns
+      // a 32 x 64 box of consecutive rows of ic3 (an expert's segment is padded to a multiple of 32 rows).  It converts chunk by chunk into its staging tile (row = lane, 16-byte chunks
       // swizzled by the row like a TMA tile, so the stores hit every bank once) and one lane hands the tile to a TMA
       // store: no exchange between lanes and no store instructions in the chain.  The staging tile is rewritten only
       // after the previous store has read it.  (The 32 KB of staging tiles cost this GEMM one of its ring slots.)
       bool by_tma = false;
-      if constexpr (MODE == 1) by_tma = p.out_sorted && ncols > 0 && tok - lane + 32 <= rows;
+      if constexpr (MODE == 1) by_tma = p.out_sorted && ncols > 0 && tok - lane < rows;
       if (by_tma) {
         // two halves of 32 columns through one 2 KB staging tile (64-byte rows, 64B swizzle): the first half's store
         // has long read the tile when the second half is converted
         const uint32_t stage = ring_u32 + ST * STAGE_BYTES + SW * W_BYTES + warp * 2048;
         const uint32_t srow = stage + lane * 64, sx = (lane >> 1) & 3;
+        const int out_row0 = info.y + p.pad_off[info.x] + tok - lane;   // rows past the tile's end land in the padding
         uint32_t v[16];
 #pragma unroll
         for (int hh = 0; hh < 2; ++hh) {
@@ -312,7 +314,7 @@ __global__ void __launch_bounds__(Roles<MODE>::THREADS, 1) grouped_gemm_kernel(c
           __syncwarp();
           if (lane == 0) {
             if (hh == 1) mbar_arrive_cluster(leader(&sh->tmem_empty[buf]));
-            tma_store_2d(&p.o_map, stage, wt * ITEM_N + n_base + 32 * hh, info.y + tok - lane);
+            tma_store_2d(&p.o_map, stage, wt * ITEM_N + n_base + 32 * hh, out_row0);
             bulk_commit();
           }
         }
@@ -640,10 +642,14 @@ __global__ void __launch_bounds__(Roles<MODE>::THREADS, 1) grouped_gemm_kernel(c
 // rows, run as M = 128 over the pair.  Full tiles first, then the 129..255-row tiles, then the half tiles, so that
 // the static round-robin hands every CTA pair a similar mix.
 __global__ void __launch_bounds__(1024) build_ttiles_kernel(const int32_t* __restrict__ offsets, int num_slots,
-                                                            int4* __restrict__ tiles, int32_t* __restrict__ num_tiles) {
+                                                            int4* __restrict__ tiles, int32_t* __restrict__ num_tiles,
+                                                            int32_t* __restrict__ pad_off) {
   // thread e: expert e (num_slots <= 1024).  Exclusive scans of the three tile counts over the experts: warp
-  // shuffles, then the warp totals.
-  __shared__ int32_t wtot[3][32];
+  // shuffles, then the warp totals.  A fourth scan gives pad_off[e]: how far expert e's rows are shifted in the
+  // per-route output of the down GEMM, where every expert's segment is padded to a multiple of 32 rows (so that any
+  // 32 consecutive tile rows can be written as one box).
+  constexpr int NC = 4;
+  __shared__ int32_t wtot[NC][32];
   const int e = threadIdx.x, lane = e & 31, warp = e >> 5;
   int begin = 0, cnt = 0;
   if (e < num_slots) {
@@ -651,22 +657,22 @@ __global__ void __launch_bounds__(1024) build_ttiles_kernel(const int32_t* __res
     cnt = offsets[e + 1] - begin;
   }
   const int rem = cnt % TN;
-  const int n[3] = {cnt / TN, rem > TN / 2 ? 1 : 0, (rem > 0 && rem <= TN / 2) ? 1 : 0};
-  int sc[3] = {n[0], n[1], n[2]};  // inclusive scans inside the warp
+  const int n[NC] = {cnt / TN, rem > TN / 2 ? 1 : 0, (rem > 0 && rem <= TN / 2) ? 1 : 0, (32 - (cnt & 31)) & 31};
+  int sc[NC] = {n[0], n[1], n[2], n[3]};  // inclusive scans inside the warp
 #pragma unroll
   for (int o = 1; o < 32; o <<= 1) {
 #pragma unroll
-    for (int c = 0; c < 3; ++c) {
+    for (int c = 0; c < NC; ++c) {
       const int a = __shfl_up_sync(0xffffffffu, sc[c], o);
       if (lane >= o) sc[c] += a;
     }
   }
   if (lane == 31)
-    for (int c = 0; c < 3; ++c) wtot[c][warp] = sc[c];
+    for (int c = 0; c < NC; ++c) wtot[c][warp] = sc[c];
   __syncthreads();
-  int before[3] = {0, 0, 0}, total[3] = {0, 0, 0};
+  int before[NC] = {0, 0, 0, 0}, total[NC] = {0, 0, 0, 0};
   for (int w = 0; w < 32; ++w)
-    for (int c = 0; c < 3; ++c) {
+    for (int c = 0; c < NC; ++c) {
       if (w < warp) before[c] += wtot[c][w];
       total[c] += wtot[c][w];
     }
@@ -676,6 +682,7 @@ __global__ void __launch_bounds__(1024) build_ttiles_kernel(const int32_t* __res
     for (int i = 0; i < n[0]; ++i, ++o) tiles[o] = make_int4(e, begin + i * TN, TN, 0);
     if (n[1]) tiles[total[0] + before[1] + sc[1] - 1] = make_int4(e, begin + cnt - rem, rem, 0);
     if (n[2]) tiles[total[0] + total[1] + before[2] + sc[2] - 1] = make_int4(e, begin + cnt - rem, rem, 1);
+    pad_off[e] = before[3] + sc[3] - n[3];
   }
 }
 
@@ -795,7 +802,8 @@ __global__ void __launch_bounds__(256) scatter_rows_f16_kernel(const __nv_bfloat
 // out[t] = bf16(sum_k f32(ic3[t,k])) in k order; optional merge with the shared expert.
 template <int TOPK>
 __global__ void __launch_bounds__(256) combine_kernel(const __nv_bfloat16* __restrict__ ic3,
-                                                      const int32_t* __restrict__ inv,  // route -> row of ic3 (-1: none) or null
+                                                      const int32_t* __restrict__ inv,  // route -> sorted position (-1: none) or null
+                                                      const int32_t* __restrict__ pad_off,  // with inv: row = position + pad_off[id]
                                                       const int32_t* __restrict__ ids, int num_slots, int T,
                                                       int top_k, int H, const __nv_bfloat16* __restrict__ shared,
                                                       const __nv_bfloat16* __restrict__ gate,
@@ -826,7 +834,7 @@ __global__ void __launch_bounds__(256) combine_kernel(const __nv_bfloat16* __res
       if (inv != nullptr) {   // rows in sorted order: the permutation's inverse says where (and whether) a route landed
         const int pos = inv[(int64_t)t * TOPK + k];
         live[k] = pos >= 0;
-        row[k] = pos;
+        row[k] = live[k] ? pos + pad_off[ids[(int64_t)t * TOPK + k]] : 0;
       } else if (ids != nullptr) {
         const int id = ids[(int64_t)t * TOPK + k];
         live[k] = id >= 0 && id < num_slots;  // dropped route: its ic3 row was never written
@@ -846,7 +854,7 @@ __global__ void __launch_bounds__(256) combine_kernel(const __nv_bfloat16* __res
       if (inv != nullptr) {
         const int pos = inv[row];
         if (pos < 0) continue;
-        row = pos;
+        row = pos + pad_off[ids[row]];
       } else if (ids != nullptr) {
         const int id = ids[row];
         if (id < 0 || id >= num_slots) continue;
@@ -869,13 +877,13 @@ __global__ void __launch_bounds__(256) combine_kernel(const __nv_bfloat16* __res
       make_uint4(pack_bf16x2(acc[0], acc[1]), pack_bf16x2(acc[2], acc[3]), pack_bf16x2(acc[4], acc[5]), pack_bf16x2(acc[6], acc[7]));
 }
 
-static int launch_combine(const __nv_bfloat16* ic3, const int32_t* inv, const int32_t* ids, int num_slots, int T, int top_k,
-                          int H, const __nv_bfloat16* shared, const __nv_bfloat16* gate, __nv_bfloat16* out, cudaStream_t st) {
+static int launch_combine(const __nv_bfloat16* ic3, const int32_t* inv, const int32_t* pad_off, const int32_t* ids,
+                          int num_slots, int T, int top_k, int H, const __nv_bfloat16* shared, const __nv_bfloat16* gate, __nv_bfloat16* out, cudaStream_t st) {
   const int64_t groups = (int64_t)T * (H / 8);
   const unsigned grid = (unsigned)((groups + 255) / 256);
-  if (top_k == 8) combine_kernel<8><<<grid, 256, 0, st>>>(ic3, inv, ids, num_slots, T, top_k, H, shared, gate, out);
-  else if (top_k == 1) combine_kernel<1><<<grid, 256, 0, st>>>(ic3, inv, ids, num_slots, T, top_k, H, shared, gate, out);
-  else combine_kernel<0><<<grid, 256, 0, st>>>(ic3, inv, ids, num_slots, T, top_k, H, shared, gate, out);
+  if (top_k == 8) combine_kernel<8><<<grid, 256, 0, st>>>(ic3, inv, pad_off, ids, num_slots, T, top_k, H, shared, gate, out);
+  else if (top_k == 1) combine_kernel<1><<<grid, 256, 0, st>>>(ic3, inv, pad_off, ids, num_slots, T, top_k, H, shared, gate, out);
+  else combine_kernel<0><<<grid, 256, 0, st>>>(ic3, inv, pad_off, ids, num_slots, T, top_k, H, shared, gate, out);
   return check_launch();
 }
 
@@ -909,7 +917,7 @@ __global__ void silu_and_mul_kernel(const __nv_bfloat16* __restrict__ in, __nv_b
 struct PrefillWs {
   void* perm_ws;
   int64_t perm_bytes;
-  int32_t *sorted_routes, *inv_routes, *offsets, *num_mtiles;
+  int32_t *sorted_routes, *inv_routes, *offsets, *num_mtiles, *pad_off;
   int4* mtiles;
   __half *xs, *ic2;
   float* a_inv;
@@ -928,11 +936,12 @@ static PrefillWs carve_prefill_ws(void* ws, int T, int top_k, int H, int I, int 
   w.inv_routes = reinterpret_cast<int32_t*>(p + off); off += up(R * 4);
   w.offsets = reinterpret_cast<int32_t*>(p + off); off += up(((int64_t)slots + 2) * 4);
   w.num_mtiles = reinterpret_cast<int32_t*>(p + off); off += up(16);
+  w.pad_off = reinterpret_cast<int32_t*>(p + off); off += up(((int64_t)slots + 1) * 4);
   w.mtiles = reinterpret_cast<int4*>(p + off); off += up((R / TN + slots + 2) * 16);
   w.a_inv = reinterpret_cast<float*>(p + off); off += up((R + TN) * 4);
   w.xs = reinterpret_cast<__half*>(p + off); off += up((R + TN) * H * 2);
   w.ic2 = reinterpret_cast<__half*>(p + off); off += up((R + TN) * I * 2);
-  w.ic3 = reinterpret_cast<__nv_bfloat16*>(p + off); off += up(R * H * 2);
+  w.ic3 = reinterpret_cast<__nv_bfloat16*>(p + off); off += up((R + 32 * (int64_t)slots) * H * 2);  // segments padded to 32 rows
   w.bytes = off;
   return w;
 }
@@ -1117,7 +1126,7 @@ static int prefill_stages_impl(const void* x, const b200moe_banks* banks, const 
     rc = permute_with_inverse(topk_ids, R, S, 1, nullptr, 0, nullptr, 0, nullptr, ws.sorted_routes, ws.offsets,
                               ws.inv_routes, ws.perm_ws, ws.perm_bytes, stream);
     if (rc) return rc;
-    build_ttiles_kernel<<<1, 1024, 0, st>>>(ws.offsets, S, ws.mtiles, ws.num_mtiles);
+    build_ttiles_kernel<<<1, 1024, 0, st>>>(ws.offsets, S, ws.mtiles, ws.num_mtiles, ws.pad_off);
     if ((rc = check_launch())) return rc;
     if (by_token)
       scatter_rows_f16_kernel<<<(unsigned)(((int64_t)T * 32 + 255) / 256), 256, 0, st>>>(
@@ -1186,13 +1195,14 @@ static int prefill_stages_impl(const void* x, const b200moe_banks* banks, const 
   // in route order when they go to their home GPUs or when the caller reads them (B200MOE_STAGE_ROUTE_ORDER).
   const bool sorted_out = out_peers == nullptr && !(stage_mask & B200MOE_STAGE_ROUTE_ORDER);
   g2.out_sorted = sorted_out;
-  if (sorted_out && (rc = encode_rows_map(&g2.o_map, ws.ic3, R, H, H, 32, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 32, CU_TENSOR_MAP_SWIZZLE_64B))) return rc;
+  g2.pad_off = ws.pad_off;
+  if (sorted_out && (rc = encode_rows_map(&g2.o_map, ws.ic3, (int64_t)R + 32 * (int64_t)S, H, H, 32, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 32, CU_TENSOR_MAP_SWIZZLE_64B))) return rc;
   if (stage_mask & B200MOE_STAGE_GEMM2) {
     rc = launch_grouped_gemm<1>(g2, (int)std::min<int64_t>(pairs, (int64_t)max_mtiles * g2.NT), st);
     if (rc) return rc;
   }
   if (stage_mask & B200MOE_STAGE_COMBINE) {
-    rc = launch_combine(ws.ic3, sorted_out ? ws.inv_routes : nullptr, topk_ids, S, T, top_k, H,
+    rc = launch_combine(ws.ic3, sorted_out ? ws.inv_routes : nullptr, ws.pad_off, topk_ids, S, T, top_k, H,
                         reinterpret_cast<const __nv_bfloat16*>(shared),
                         reinterpret_cast<const __nv_bfloat16*>(shared_gate_logit), reinterpret_cast<__nv_bfloat16*>(out), st);
     if (rc) return rc;
@@ -1253,7 +1263,7 @@ extern "C" int b200moe_shared_epilogue(const void* routed, const void* shared, c
   if (!routed || !shared || !gate || !out) return B200MOE_E_NULL;
   if (T < 0 || H < 8 || H % 8) return B200MOE_E_SHAPE;
   if (!aligned16(routed) || !aligned16(shared) || !aligned16(out)) return B200MOE_E_ALIGN;
-  return launch_combine(reinterpret_cast<const __nv_bfloat16*>(routed), nullptr, nullptr, 0, T, 1, H,
+  return launch_combine(reinterpret_cast<const __nv_bfloat16*>(routed), nullptr, nullptr, nullptr, 0, T, 1, H,
                         reinterpret_cast<const __nv_bfloat16*>(shared), reinterpret_cast<const __nv_bfloat16*>(gate),
                         reinterpret_cast<__nv_bfloat16*>(out), reinterpret_cast<cudaStream_t>(stream));
 }
@@ -1263,7 +1273,7 @@ extern "C" int b200moe_sum_routes(const void* in, void* out, int T, int top_k, i
   if (!in || !out) return B200MOE_E_NULL;
   if (T < 0 || top_k < 1 || H < 8 || H % 8) return B200MOE_E_SHAPE;
   if (!aligned16(in) || !aligned16(out)) return B200MOE_E_ALIGN;
-  return launch_combine(reinterpret_cast<const __nv_bfloat16*>(in), nullptr, nullptr, 0, T, top_k, H, nullptr, nullptr,
+  return launch_combine(reinterpret_cast<const __nv_bfloat16*>(in), nullptr, nullptr, nullptr, 0, T, top_k, H, nullptr, nullptr,
                         reinterpret_cast<__nv_bfloat16*>(out), reinterpret_cast<cudaStream_t>(stream));
 }
 
@@ -1274,7 +1284,7 @@ extern "C" int b200moe_combine_routes(const void* ic3, const int32_t* topk_ids, 
   if ((shared == nullptr) != (shared_gate_logit == nullptr)) return B200MOE_E_NULL;
   if (T < 0 || top_k < 1 || H < 8 || H % 8) return B200MOE_E_SHAPE;
   if (!aligned16(ic3) || !aligned16(out) || (shared && !aligned16(shared))) return B200MOE_E_ALIGN;
-  return launch_combine(reinterpret_cast<const __nv_bfloat16*>(ic3), nullptr, topk_ids, num_slots, T, top_k, H,
+  return launch_combine(reinterpret_cast<const __nv_bfloat16*>(ic3), nullptr, nullptr, topk_ids, num_slots, T, top_k, H,
                         reinterpret_cast<const __nv_bfloat16*>(shared), reinterpret_cast<const __nv_bfloat16*>(shared_gate_logit),
                         reinterpret_cast<__nv_bfloat16*>(out), reinterpret_cast<cudaStream_t>(stream));
 }
