@@ -51,9 +51,6 @@ constexpr int WROWS = 128;                           // weight rows a CTA unpack
 constexpr int ITEM_N = 2 * WROWS;                    // weight rows per item (the MMA's N)
 constexpr int TN = 2 * TOK_ROWS;                     // tokens per full tile
 constexpr int A_BYTES = TOK_ROWS * BK * 2, B_BYTES = WROWS * BK * 2;
-#ifndef B200MOE_DIRECT_ARRIVE
-#define B200MOE_DIRECT_ARRIVE 1
-#endif
 #ifndef B200MOE_ST1
 #define B200MOE_ST1 4
 #endif
@@ -100,6 +97,7 @@ struct GgParams {
   const int32_t* num_mtiles;
   const int32_t* sorted_routes;  // sorted position -> flat route id
   const float* topk_w;           // [routes]
+  const float* w_sorted;         // mode 1: router weight by sorted position
   const float* a_inv;            // mode 0: inverse of the power-of-two scale of every token row
   void* out;                     // mode 0: ic2 [pos, half_n] fp16; mode 1: ic3 bf16, [route, N] or [pos, N] (out_sorted)
   CUtensorMap o_map;             // mode 1, out_sorted: ic3 [pos, N] as 32-column x 32-row boxes, 64B swizzle
@@ -113,8 +111,8 @@ struct GgParams {
 };
 
 struct alignas(16) GgShared {
-  unsigned long long full[ST_MAX], empty[ST_MAX], part[ST_MAX], full_w[SW], empty_w[SW];
-  unsigned long long tmem_full[2], tmem_empty[2], table[2];
+  unsigned long long full[ST_MAX], empty[ST_MAX], full_w[SW], empty_w[SW];
+  unsigned long long tmem_full[2], tmem_empty[2], table[2], table_empty[2];
   uint32_t tmem_base;
   int abort_flag;
   alignas(16) float gl[2][ITEM_N];  // per accumulator buffer: the fp32 global of every column of the item
@@ -125,6 +123,12 @@ constexpr size_t GG_SMEM = 1024 + (size_t)ST_MAX * STAGE_BYTES + (size_t)SW * W_
 // it spends in its waits and in its work; read back with b200moe_debug_gg_profile.
 #ifdef B200MOE_GG_PROFILE
 __device__ long long g_gg_prof[2][32];
+__device__ unsigned long long g_gg_pairs[2][2][160];   // [mode][start | end][CTA]: globaltimer, ns
+B200MOE_DEVICE unsigned long long gtimer() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
 #define PROF_DECL(n) long long prof[n] = {};
 #define PROF_T(var) const long long var = clock64();
 #define PROF_ADD(slot, a, b) prof[slot] += (b) - (a);
@@ -150,20 +154,23 @@ __global__ void __launch_bounds__(Roles<MODE>::THREADS, 1) grouped_gemm_kernel(c
   const int rank = (int)cluster_ctarank();
   const int unit = (int)(blockIdx.x >> 1), units = (int)(gridDim.x >> 1);
 
+#ifdef B200MOE_GG_PROFILE
+  if (tid == 0 && blockIdx.x < 160) g_gg_pairs[MODE][0][blockIdx.x] = gtimer();
+  const long long clk_start = clock64();
+#endif
   if (tid == 0) {
     for (int s = 0; s < ST; ++s) {
-      // the leader's byte-count arrive (+ the bytes of both CTAs) and either one relay per CTA or every unpack warp of the
-      // k-step's group in both CTAs
-      mbar_init(smem_u32(&sh->full[s]), B200MOE_DIRECT_ARRIVE ? 1 + 2 * GROUP_WARPS : 3);
+      // the leader's byte-count arrive (+ the bytes of both CTAs) and every unpack warp of the k-step's group in both CTAs
+      mbar_init(smem_u32(&sh->full[s]), 1 + 2 * GROUP_WARPS);
       mbar_init(smem_u32(&sh->empty[s]), 1);             // the MMA thread's commit
-      mbar_init(smem_u32(&sh->part[s]), GROUP_WARPS);    // this CTA's unpack warps of the k-step's group
     }
     for (int s = 0; s < SW; ++s) {
       mbar_init(smem_u32(&sh->full_w[s]), 1);            // the weight TMA thread's byte-count arrive (+ bytes)
       mbar_init(smem_u32(&sh->empty_w[s]), R::UNPACK_WARPS * (SUPER / R::GROUPS));  // one arrival per unpack warp and visit
     }
     for (int b = 0; b < 2; ++b) {
-      mbar_init(smem_u32(&sh->table[b]), EPI_WARPS * 32);
+      mbar_init(smem_u32(&sh->table[b]), 1);                 // the table warp has filled gl[b]
+      mbar_init(smem_u32(&sh->table_empty[b]), EPI_WARPS);   // every epilogue warp has read gl[b] for the last time
       mbar_init(smem_u32(&sh->tmem_full[b]), 1);
       mbar_init(smem_u32(&sh->tmem_empty[b]), 2 * EPI_WARPS);
     }
@@ -202,6 +209,7 @@ __global__ void __launch_bounds__(Roles<MODE>::THREADS, 1) grouped_gemm_kernel(c
     int tl = 0;
     PROF_DECL(6)
     for (int item = unit; item < total_items; item += units, ++tl) {
+      PROF_T(p0)
       const int tt = item / NT, wt = item - tt * NT;
       const int4 info = p.mtiles[tt];
       const int buf = tl & 1, rows = info.z, half = info.w;
@@ -216,22 +224,15 @@ __global__ void __launch_bounds__(Roles<MODE>::THREADS, 1) grouped_gemm_kernel(c
       const int n_base = col0 + (half ? (q >> 1) * (ITEM_N / 2) : 0);  // item column behind TMEM column col0
       const bool valid = tok < rows && ncols > 0;
       const int pos = info.y + (valid ? tok : 0);
-      // the item's per-column globals -> shared memory (one pass of the epilogue threads), then a (bounded) barrier
-      // among the epilogue threads: a table is rewritten two items later, after every warp has passed the next one
-      {
-        const float* gsrc = p.globals + (int64_t)info.x * (p.global_stride >> 2);
-        for (int c = tid; c < ITEM_N; c += EPI_WARPS * 32) sh->gl[buf][c] = gsrc[weight_row(wt, c)];
-        mbar_arrive(smem_u32(&sh->table[buf]));
-        if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&sh->table[buf]), (tl >> 1) & 1, abort_flag))) break;
-      }
-      float mul = 0.f;          // mode 0: inverse token scale; mode 1: router weight
+      // mode 0: inverse token scale; mode 1: router weight -- both by sorted position
+      const float mul = (MODE == 0 ? p.a_inv : p.w_sorted)[pos];
+      // the item's per-column globals are in gl[buf] once the table warp says so (bounded wait)
+      if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&sh->table[buf]), (tl >> 1) & 1, abort_flag))) break;
       char* dst = nullptr;      // first byte of this thread's outputs for item column n_base; null = no token here
       if (MODE == 0) {
-        mul = p.a_inv[pos];
         dst = reinterpret_cast<char*>(p.out) + ((int64_t)pos * p.half_n + wt * (ITEM_N / 2) + (n_base >> 1)) * 2;
-      } else {
+      } else if (!p.out_sorted) {
         const int route = p.sorted_routes[pos];
-        mul = p.topk_w[route];
         __nv_bfloat16* base = reinterpret_cast<__nv_bfloat16*>(p.out) + (int64_t)route * p.N;
         if (p.out_peers != nullptr) {  // the row goes straight to the token's home GPU over NVLink
           int64_t groute = route + p.route_offset;
@@ -243,6 +244,7 @@ __global__ void __launch_bounds__(Roles<MODE>::THREADS, 1) grouped_gemm_kernel(c
       }
       if (!valid) dst = nullptr;
       PROF_T(e0)
+      PROF_ADD(3, p0, e0)
       const bool ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&sh->tmem_full[buf]), (tl >> 1) & 1, abort_flag));
       if (!ok) break;
       PROF_T(e1)
@@ -313,7 +315,10 @@ __global__ void __launch_bounds__(Roles<MODE>::THREADS, 1) grouped_gemm_kernel(c
           asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
           __syncwarp();
           if (lane == 0) {
-            if (hh == 1) mbar_arrive_cluster(leader(&sh->tmem_empty[buf]));
+            if (hh == 1) {
+              mbar_arrive_cluster(leader(&sh->tmem_empty[buf]));
+              mbar_arrive(smem_u32(&sh->table_empty[buf]));
+            }
             tma_store_2d(&p.o_map, stage, wt * ITEM_N + n_base + 32 * hh, out_row0);
             bulk_commit();
           }
@@ -371,7 +376,10 @@ __global__ void __launch_bounds__(Roles<MODE>::THREADS, 1) grouped_gemm_kernel(c
       PROF_T(e15)
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive_cluster(leader(&sh->tmem_empty[buf]));
+      if (lane == 0) {
+        mbar_arrive_cluster(leader(&sh->tmem_empty[buf]));
+        mbar_arrive(smem_u32(&sh->table_empty[buf]));
+      }
       PROF_T(e2)
       PROF_ADD(0, e0, e1) PROF_ADD(1, e1, e2) PROF_ADD(2, 0, 1) PROF_ADD(5, e15, e2)
     }
@@ -415,10 +423,7 @@ __global__ void __launch_bounds__(Roles<MODE>::THREADS, 1) grouped_gemm_kernel(c
       if (!PRE_UNPACK) release();
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       __syncwarp();
-      if (lane == 0) {
-        if (B200MOE_DIRECT_ARRIVE) mbar_arrive_cluster(leader(&sh->full[s]));
-        else mbar_arrive(smem_u32(&sh->part[s]));
-      }
+      if (lane == 0) mbar_arrive_cluster(leader(&sh->full[s]));
       return true;
     };
     if (p.w_staged) {
@@ -551,15 +556,21 @@ __global__ void __launch_bounds__(Roles<MODE>::THREADS, 1) grouped_gemm_kernel(c
       }
     }
   } else if (warp == R::RELAY) {
-    // ------------------------------------------------------------------ relay: this CTA's weight half of a k-step -> leader
-    // (no proxy fence here: the unpackers fenced their own stores)
-    if (lane == 0 && !B200MOE_DIRECT_ARRIVE) {
-      const uint32_t leader_full = leader(&sh->full[0]);
-      for (uint32_t it = 0; it < total_steps; ++it) {
-        const int s = it % ST;
-        if (!mbar_wait(smem_u32(&sh->part[s]), (it / ST) & 1, abort_flag)) break;
-        mbar_arrive_cluster(leader_full + s * 8);
-      }
+    // ------------------------------------------------------------------ table warp: per-column globals of an item -> gl[buf]
+    // (two items ahead of the epilogue at most; the epilogue warps only wait for it, not for one another)
+    int tlr = 0;
+    for (int item = unit; item < total_items; item += units, ++tlr) {
+      const int buf = tlr & 1;
+      if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&sh->table_empty[buf]), ((tlr >> 1) & 1) ^ 1, abort_flag))) break;
+      const int tt = item / NT, wt = item - tt * NT;
+      const float* gsrc = p.globals + (int64_t)p.mtiles[tt].x * (p.global_stride >> 2);
+      float g[ITEM_N / 32];
+#pragma unroll
+      for (int i = 0; i < ITEM_N / 32; ++i) g[i] = gsrc[weight_row(wt, lane + 32 * i)];
+#pragma unroll
+      for (int i = 0; i < ITEM_N / 32; ++i) sh->gl[buf][lane + 32 * i] = g[i];
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&sh->table[buf]));
     }
   } else {
     // ------------------------------------------------------------------ MMA issuer (the pair's leader only)
@@ -636,6 +647,10 @@ __global__ void __launch_bounds__(Roles<MODE>::THREADS, 1) grouped_gemm_kernel(c
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)TMEM_COLS) : "memory");
   }
+#ifdef B200MOE_GG_PROFILE
+  if (tid == 0 && blockIdx.x < 160) g_gg_pairs[MODE][1][blockIdx.x] = gtimer();
+  if (tid == 0 && blockIdx.x == 0) g_gg_prof[MODE][31] = clock64() - clk_start;
+#endif
 }
 
 // Token-tile list of the grouped GEMM: {slot, first sorted position, rows <= 256, half}.  half = 1: at most 128
@@ -694,11 +709,13 @@ __global__ void __launch_bounds__(256) gather_rows_f16_kernel(const __nv_bfloat1
                                                               const __nv_bfloat16* const* __restrict__ src_peers,
                                                               int tokens_per_rank, const int32_t* __restrict__ sorted_routes,
                                                               const int32_t* __restrict__ offsets, int num_slots, int top_k,
-                                                              int H, __half* __restrict__ xs, float* __restrict__ inv_out) {
+                                                              int H, __half* __restrict__ xs, float* __restrict__ inv_out,
+                                                              const float* __restrict__ topk_w, float* __restrict__ w_sorted) {
   const int lane = threadIdx.x & 31;
   const int64_t pos = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   if (pos >= offsets[num_slots]) return;
   const int token = sorted_routes[pos] / top_k;
+  if (lane == 0) w_sorted[pos] = topk_w[sorted_routes[pos]];
   const __nv_bfloat16* row;
   if (src_peers != nullptr) row = src_peers[token / tokens_per_rank] + (int64_t)(token % tokens_per_rank) * lda;
   else row = x + (int64_t)token * lda;
@@ -750,11 +767,14 @@ __global__ void __launch_bounds__(256) gather_rows_f16_kernel(const __nv_bfloat1
 // here).  Reads T rows instead of top_k x T; the writes are the same.  Rows of up to 2048 elements.
 __global__ void __launch_bounds__(256) scatter_rows_f16_kernel(const __nv_bfloat16* __restrict__ x, int64_t lda, int T,
                                                                const int32_t* __restrict__ inv_routes, int top_k, int H,
-                                                               __half* __restrict__ xs, float* __restrict__ inv_out) {
+                                                               __half* __restrict__ xs, float* __restrict__ inv_out,
+                                                               const float* __restrict__ topk_w,
+                                                               float* __restrict__ w_sorted) {
   const int lane = threadIdx.x & 31;
   const int64_t t = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   if (t >= T) return;
   int my_pos = lane < top_k ? inv_routes[t * top_k + lane] : -1;   // lane k holds the position of route k
+  if (my_pos >= 0) w_sorted[my_pos] = topk_w[t * top_k + lane];     // router weights in sorted order, for the down GEMM
   if (__ballot_sync(0xffffffffu, my_pos >= 0) == 0u) return;         // none of the token's experts lives here
   const __nv_bfloat16* row = x + t * lda;
   const uint64_t stream = l2_policy_stream();
@@ -920,7 +940,7 @@ struct PrefillWs {
   int32_t *sorted_routes, *inv_routes, *offsets, *num_mtiles, *pad_off;
   int4* mtiles;
   __half *xs, *ic2;
-  float* a_inv;
+  float *a_inv, *w_sorted;
   __nv_bfloat16* ic3;
   int64_t bytes;
 };
@@ -939,6 +959,7 @@ static PrefillWs carve_prefill_ws(void* ws, int T, int top_k, int H, int I, int 
   w.pad_off = reinterpret_cast<int32_t*>(p + off); off += up(((int64_t)slots + 1) * 4);
   w.mtiles = reinterpret_cast<int4*>(p + off); off += up((R / TN + slots + 2) * 16);
   w.a_inv = reinterpret_cast<float*>(p + off); off += up((R + TN) * 4);
+  w.w_sorted = reinterpret_cast<float*>(p + off); off += up((R + TN) * 4);
   w.xs = reinterpret_cast<__half*>(p + off); off += up((R + TN) * H * 2);
   w.ic2 = reinterpret_cast<__half*>(p + off); off += up((R + TN) * I * 2);
   w.ic3 = reinterpret_cast<__nv_bfloat16*>(p + off); off += up((R + 32 * (int64_t)slots) * H * 2);  // segments padded to 32 rows
@@ -1000,6 +1021,9 @@ static int encode_bank_map(CUtensorMap* map, const void* base, int64_t slots, in
 using namespace b200moe;
 
 #ifdef B200MOE_GG_PROFILE
+extern "C" int b200moe_debug_gg_pairs(unsigned long long* host_out) {
+  return (int)cudaMemcpyFromSymbol(host_out, g_gg_pairs, sizeof(unsigned long long) * 2 * 2 * 160);
+}
 extern "C" int b200moe_debug_gg_profile(long long* host_out) {
   return (int)cudaMemcpyFromSymbol(host_out, g_gg_prof, sizeof(long long) * 2 * 32);
 }
@@ -1130,10 +1154,11 @@ static int prefill_stages_impl(const void* x, const b200moe_banks* banks, const 
     if ((rc = check_launch())) return rc;
     if (by_token)
       scatter_rows_f16_kernel<<<(unsigned)(((int64_t)T * 32 + 255) / 256), 256, 0, st>>>(
-          reinterpret_cast<const __nv_bfloat16*>(x), H, T, ws.inv_routes, top_k, H, ws.xs, ws.a_inv);
+          reinterpret_cast<const __nv_bfloat16*>(x), H, T, ws.inv_routes, top_k, H, ws.xs, ws.a_inv, topk_weights, ws.w_sorted);
     else
       gather_rows_f16_kernel<<<(unsigned)(((int64_t)R * 32 + 255) / 256), 256, 0, st>>>(
-          reinterpret_cast<const __nv_bfloat16*>(x), H, nullptr, 1, ws.sorted_routes, ws.offsets, S, top_k, H, ws.xs, ws.a_inv);
+          reinterpret_cast<const __nv_bfloat16*>(x), H, nullptr, 1, ws.sorted_routes, ws.offsets, S, top_k, H, ws.xs, ws.a_inv,
+          topk_weights, ws.w_sorted);
     if ((rc = check_launch())) return rc;
   }
 
@@ -1161,6 +1186,7 @@ static int prefill_stages_impl(const void* x, const b200moe_banks* banks, const 
   g1.sorted_routes = ws.sorted_routes;
   g1.topk_w = topk_weights;
   g1.a_inv = ws.a_inv;
+  g1.w_sorted = ws.w_sorted;
   g1.out = ws.ic2;
   g1.status = status;
   if (stage_mask & B200MOE_STAGE_GEMM1) {
