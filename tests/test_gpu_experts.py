@@ -351,3 +351,20 @@ def test_prefill_graphs_replay_the_eager_result_for_refilled_buffers():
         got = graphs(xb, ob)
         assert got is ob and torch.equal(got.view(torch.int16), want.view(torch.int16))
     assert len(graphs.graphs) == 2
+
+
+@pytest.mark.parametrize("hidden,top_k,t", [(4096, 2, 70), (512, 1, 333), (2048, 8, 257)])
+def test_prefill_other_row_lengths_and_route_counts(hidden, top_k, t):
+    """Rows longer than a warp keeps in registers take the per-position copy kernel; top_k = 1 and the full-size
+    row length take the per-token one.  Same parity gate, dropped routes included."""
+    shape = synth.Shape(hidden=hidden, intermediate=256, num_experts=8, top_k=top_k, shared_intermediate=128)
+    layer = synth.make_layer(90 + top_k, t, shape)
+    w, ids = oracle.router_topk(synth.router_logits(layer["x"], layer["router_w"]), shape.top_k)
+    ids[3, 0] = -1
+    want = oracle.moe_experts_bf16(layer["x"], layer, w, ids)
+    d = _cuda(layer)
+    got = ops.prefill_experts(d["x"], _banks(d), w.to(DEV), ids.to(DEV), check_status=True)
+    _assert_parity(got, want, f"prefill H={hidden} top_k={top_k}")
+    rows = ops.prefill_route_rows(d["x"], _banks(d), w.to(DEV), ids.to(DEV))        # route order on request
+    summed = ops.combine_routes(rows, ids.to(DEV), shape.num_experts)
+    assert torch.equal(summed.view(torch.int16), got.view(torch.int16))
