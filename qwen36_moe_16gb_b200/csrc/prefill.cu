@@ -3,8 +3,9 @@
 // One work item = (token tile of one expert, 256 weight rows), computed by a PAIR of CTAs (cluster of two,
 // tcgen05 cta_group::2) as D[tokens x 256 weight rows] += A[tokens x 64] * B[256 x 64]^T per k-step, kind::f16
 // with fp16 operands, fp32 accumulation.
-//   A = token rows, fp16.  They are contiguous: a pre-pass gathers x through the permutation into expert order,
-//       scaled per row by a power of two into fp16 range (exact; the epilogue multiplies the inverse back); the
+//   A = token rows, fp16.  They are contiguous: a pre-pass copies x into expert order (one warp per token writes the
+//       row to the sorted position of each of its routes), scaled per row by a power of two into fp16 range (exact;
+//       the epilogue multiplies the inverse back); the
 //       down GEMM reads the ic2 rows the gate_up GEMM wrote, already in expert order.  One thread per CTA asks the
 //       TMA unit for boxes of 64 rows x 64 k (128-byte swizzle).  Each CTA of the pair holds its own token rows:
 //       128 of a 256-token tile, or 64 of a tile with at most 128 tokens (M = 128 over the pair costs half the
@@ -18,21 +19,24 @@
 //       the SM's load/store pipe (one line per cycle, shared with every shared-memory store) was the bottleneck
 //       of that form; a proxy fence or barrier arrive also waits for the thread's loads.
 //   D   TMEM lane = token, column = weight row: an epilogue thread owns ONE token and reads consecutive output
-//       columns, so SwiGLU pairs sit in one thread (gate and up rows interleave inside an item).  Four lanes
-//       exchange their pieces before they store, so that one store instruction writes whole 128-byte lines.
-//       The fp32 per-row global, the SwiGLU and the router weight are applied here with the reference's bf16
-//       rounding points.
+//       columns, so SwiGLU pairs sit in one thread (gate and up rows interleave inside an item).  gate_up: four
+//       lanes exchange their pieces before they store, so that one store instruction writes whole sectors.  down:
+//       the per-route rows stay in (padded) expert order, a warp's 32 rows are consecutive, and they leave by TMA
+//       store from a swizzled staging tile; rows bound for another GPU or wanted in route order take the exchange
+//       + store path.  The fp32 per-row global, the SwiGLU and the router weight are applied here with the
+//       reference's bf16 rounding points.
 // The MMA time of an instruction is proportional to N and independent of M (measured: 128 cycles for N = 256,
 // 64 for N = 128, for M = 128 as for M = 64 rows per CTA), so weights fill N and the tokens stream through M.
 //
 // Warp roles (one persistent CTA pair per two SMs, static round-robin over the item list):
-//   epilogue warps   TMEM -> registers -> global; warp w may touch TMEM lanes 32 (w % 4) .. +31
-//   16 unpack warps  four groups of four; group g fills the B slot of the k-steps with index = g mod 4, one thread
-//                    per weight row (64 k = 32 packed bytes + 4 scales), so four k-steps are in production at once
+//   epilogue warps   (4 gate_up, 16 down) TMEM -> registers -> global; warp w may touch TMEM lanes 32 (w % 4) .. +31
+//   unpack warps     groups of four (4 groups gate_up, 2 down); group g fills the B slot of the k-steps with index
+//                    = g mod groups, one thread per weight row (64 k = 32 packed bytes + 4 scales); every warp
+//                    tells the pair leader's barrier itself that its rows of the k-step are stored
 //   token TMA warp   lane 0 posts the byte count (leader) and issues this CTA's token boxes
 //   weight TMA warp  lane 0 fills the packed-weight staging ring of this CTA
-//   relay warp       lane 0 forwards "this CTA's weight half of the k-step is stored" to the leader's barrier
-//   MMA warp         lane 0 of the pair's leader issues tcgen05.mma / tcgen05.commit; the warp owns the TMEM
+//   table warp       fetches an item's 256 per-column globals into a shared-memory table, up to two items ahead
+//   MMA warp         one elected lane of the pair's leader issues tcgen05.mma / tcgen05.commit; the warp owns the TMEM
 // Every mbarrier wait is bounded: on time-out the CTA records a status word, stops, frees its TMEM.
 #include <algorithm>
 #include <cstdlib>
@@ -77,7 +81,7 @@ struct Roles {
   static constexpr int GROUPS = MODE == 0 ? 4 : 2;
   static constexpr int ST = MODE == 0 ? 5 : B200MOE_ST1;   // operand ring slots (one k-step each)
   static constexpr int UNPACK_WARPS = GROUPS * GROUP_WARPS;
-  static constexpr int UNPACK0 = EPI, TMA_A = EPI + UNPACK_WARPS, TMA_W = TMA_A + 1, RELAY = TMA_W + 1, MMA = RELAY + 1;
+  static constexpr int UNPACK0 = EPI, TMA_A = EPI + UNPACK_WARPS, TMA_W = TMA_A + 1, TABLE = TMA_W + 1, MMA = TABLE + 1;
   static constexpr int THREADS = (MMA + 1) * 32;
   static_assert(SUPER % GROUPS == 0, "a group visits every staged block the same number of times");
 };
@@ -396,8 +400,8 @@ __global__ void __launch_bounds__(Roles<MODE>::THREADS, 1) grouped_gemm_kernel(c
     const int j = rank * WROWS + l;  // row inside the item
     const uint32_t b_row = l * 128, b_x = l & 7;
     PROF_DECL(4)
-    // One row of a k-step: unpack, wait for the slot, store, fence, tell the relay.  gate_up unpacks into registers
-    // BEFORE it waits (the wait -> store -> fence -> relay chain is what the MMA thread waits for); down, with 28
+    // One row of a k-step: unpack, wait for the slot, store, fence, tell the leader.  gate_up unpacks into registers
+    // BEFORE it waits (the wait -> store -> fence -> arrive chain is what the MMA thread waits for); down, with 28
     // warps and 72 registers per thread, unpacks chunk by chunk after the wait.  `release` runs once the packed
     // registers have been consumed (the staged path frees its block there).
     constexpr bool PRE_UNPACK = MODE == 0;   // the down GEMM's 72 registers per thread do not hold the unpacked row
@@ -555,7 +559,7 @@ __global__ void __launch_bounds__(Roles<MODE>::THREADS, 1) grouped_gemm_kernel(c
         }
       }
     }
-  } else if (warp == R::RELAY) {
+  } else if (warp == R::TABLE) {
     // ------------------------------------------------------------------ table warp: per-column globals of an item -> gl[buf]
     // (two items ahead of the epilogue at most; the epilogue warps only wait for it, not for one another)
     int tlr = 0;
