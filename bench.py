@@ -30,7 +30,7 @@ EP_TOTAL_TOKENS = 65536
 NVFP4_DENSE_PEAK_TFLOPS = 9000.0  # nominal dense NVFP4 tensor peak of one B200
 # DRAM traffic of one gate_up grouped-GEMM launch at T=8192 (dram__bytes_read.sum + dram__bytes_write.sum of a
 # one-kernel ncu capture of this command with --steps 1); the JSON line names the capture it came from.
-NCU_TRAFFIC_GEMM1_T8192 = {"bytes": 758_743_552, "read": 694_361_344, "write": 64_382_208,
+NCU_TRAFFIC_GEMM1_T8192 = {"bytes": 758_626_560, "read": 694_373_632, "write": 64_252_928,
                            "capture": "ncu --set full -k regex:grouped_gemm -s 6 -c 2 on `bench.py --steps 1 --warmup 3 --no-decode "
                                       "--no-cpu --no-cache --no-sweep` (summary: profiles/grouped_gemm_prefill_T8192.md)"}
 CPU_TOKENS = 8192  # the CPU arms run the same T as the headline
