@@ -187,14 +187,10 @@ B200MOE_DEVICE void decode_gemm1_body(unsigned char* smem_raw, int bx, int r, co
     slot = ids[r];
   } else {
     pdl_wait();  // the logits come from the previous kernel
-    if (warp == 0) {
+    if (warp == 0) {  // the experts only: this kernel does not use the router weights
       const __nv_bfloat16* row = logits + (int64_t)token * E;
-      if (E <= 256) router_select<8, __nv_bfloat16>(row, E, top_k, 1, lane, sel_w, sel_id);
-      else router_select<16, __nv_bfloat16>(row, E, top_k, 1, lane, sel_w, sel_id);
-      if (bx == 0 && kk == 0 && lane < top_k) {
-        topk_w_out[token * top_k + lane] = sel_w[lane];
-        topk_ids_out[token * top_k + lane] = sel_id[lane];
-      }
+      if (E <= 256) router_select<8, __nv_bfloat16, false>(row, E, top_k, 1, lane, nullptr, sel_id);
+      else router_select<16, __nv_bfloat16, false>(row, E, top_k, 1, lane, nullptr, sel_id);
     }
     __syncthreads();
     slot = sel_id[kk];
@@ -220,6 +216,17 @@ B200MOE_DEVICE void decode_gemm1_body(unsigned char* smem_raw, int bx, int r, co
   if (ids != nullptr) pdl_wait();
   const float inv = stage_row_f16(x + (int64_t)token * H, H, xs, tid, blockDim.x, red);
   __syncthreads();
+  if (ids == nullptr && bx == 0 && kk == 0 && warp == 0) {
+    // one CTA per token publishes weights and ids for the second GEMM: the softmax runs here, while this warp's
+    // weight rows are on their way (sel_w / sel_id are not read by anyone else any more)
+    const __nv_bfloat16* row = logits + (int64_t)token * E;
+    if (E <= 256) router_select<8, __nv_bfloat16>(row, E, top_k, 1, lane, sel_w, sel_id);
+    else router_select<16, __nv_bfloat16>(row, E, top_k, 1, lane, sel_w, sel_id);
+    if (lane < top_k) {
+      topk_w_out[token * top_k + lane] = sel_w[lane];
+      topk_ids_out[token * top_k + lane] = sel_id[lane];
+    }
+  }
 
   float acc[4][4];
   acc_zero(acc);

@@ -9,7 +9,9 @@ namespace b200moe {
 // One warp, one token: fp32 softmax over E logits (lane j owns experts j, j+32, ...), then top_k rounds of
 // (highest logit, lowest id among equals); NaN logits rank as -1e30.  Writes the selected probabilities
 // (renormalised if asked) and ids, in selection order, to w_out / id_out (global or shared memory).
-template <int NPL, typename LogitT>
+// WEIGHTS = false: only the ids (no softmax; w_out is not touched and may be null) -- what a consumer that needs the
+// experts first and their weights later runs on its critical path.
+template <int NPL, typename LogitT, bool WEIGHTS = true>
 B200MOE_DEVICE void router_select(const LogitT* __restrict__ src, int E, int top_k, int renormalize, int lane,
                                   float* w_out, int32_t* id_out) {
   float raw[NPL], prob[NPL], cur[NPL];
@@ -19,19 +21,23 @@ B200MOE_DEVICE void router_select(const LogitT* __restrict__ src, int E, int top
     const int e = lane + 32 * i;
     raw[i] = e < E ? (float)src[e] : -INFINITY;
     mx = fmaxf(mx, raw[i]);  // fmaxf ignores NaN, as the reference's max reduction does
+    prob[i] = 0.f;
   }
-  mx = warp_max(mx);
-  float sum = 0.f;
+  if constexpr (WEIGHTS) {
+    mx = warp_max(mx);
+    float sum = 0.f;
+#pragma unroll
+    for (int i = 0; i < NPL; ++i) {
+      const int e = lane + 32 * i;
+      prob[i] = e < E ? expf(raw[i] - mx) : 0.f;
+      sum += prob[i];
+    }
+    sum = warp_sum(sum);
+#pragma unroll
+    for (int i = 0; i < NPL; ++i) prob[i] = prob[i] / sum;
+  }
 #pragma unroll
   for (int i = 0; i < NPL; ++i) {
-    const int e = lane + 32 * i;
-    prob[i] = e < E ? expf(raw[i] - mx) : 0.f;
-    sum += prob[i];
-  }
-  sum = warp_sum(sum);
-#pragma unroll
-  for (int i = 0; i < NPL; ++i) {
-    prob[i] = prob[i] / sum;
     const int e = lane + 32 * i;
     cur[i] = e < E ? (raw[i] == raw[i] ? raw[i] : -1e30f) : -INFINITY;
   }
@@ -101,13 +107,13 @@ B200MOE_DEVICE void router_select(const LogitT* __restrict__ src, int E, int top
     if ((k & 31) == 31 || k == top_k - 1) {  // flush a group of up to 32 selections
       const int kk = (k & ~31) + lane;
       if (kk <= k) {
-        w_out[kk] = my_w;
+        if constexpr (WEIGHTS) w_out[kk] = my_w;
         id_out[kk] = my_id;
       }
     }
   }
   __syncwarp();
-  if (renormalize) {
+  if (WEIGHTS && renormalize) {
     const float d = wsum > 0.f ? wsum : 1.f;
     for (int kk = lane; kk < top_k; kk += 32) w_out[kk] = w_out[kk] / d;  // each lane re-reads what it wrote
   }
