@@ -179,6 +179,7 @@ B200MOE_DEVICE void decode_gemm1_body(unsigned char* smem_raw, int bx, int r, co
 
   const int token = r / top_k, kk = r - token * top_k;
   int slot;
+  float inv = 1.f;
   if (ids != nullptr) {
     // `ids_settled`: the ids were written before the first kernel of this launch sequence started (the host-planned
     // offload step copies them in ahead of the layer loop).  Otherwise the previous kernel in the stream may have
@@ -186,13 +187,17 @@ B200MOE_DEVICE void decode_gemm1_body(unsigned char* smem_raw, int bx, int r, co
     if (!ids_settled) pdl_wait();
     slot = ids[r];
   } else {
+    // Resident block: the previous kernel is the dense rows, which produce the logits but not x, and which raise
+    // their launch trigger only after their own dependency wait -- so x is complete when this kernel starts and can
+    // be staged before the wait, while the dense rows are still running.
+    inv = stage_row_f16(x + (int64_t)token * H, H, xs, tid, blockDim.x, red);
     pdl_wait();  // the logits come from the previous kernel
     if (warp == 0) {  // the experts only: this kernel does not use the router weights
       const __nv_bfloat16* row = logits + (int64_t)token * E;
       if (E <= 256) router_select<8, __nv_bfloat16, false>(row, E, top_k, 1, lane, nullptr, sel_id);
       else router_select<16, __nv_bfloat16, false>(row, E, top_k, 1, lane, nullptr, sel_id);
     }
-    __syncthreads();
+    __syncthreads();  // also: every thread's part of xs is in shared memory
     slot = sel_id[kk];
   }
   constexpr int TS = G1_WARPS / KS;  // tile slots
@@ -213,15 +218,17 @@ B200MOE_DEVICE void decode_gemm1_body(unsigned char* smem_raw, int bx, int r, co
   };
   Fp4Regs ra, rb;
   if (items > 0) issue(ra, 0);  // weights: in flight across the dependency wait and while x is staged
-  if (ids != nullptr) pdl_wait();
-  const float inv = stage_row_f16(x + (int64_t)token * H, H, xs, tid, blockDim.x, red);
-  __syncthreads();
-  if (ids == nullptr && bx == 0 && kk == 0 && warp == 0) {
-    // one CTA per token publishes weights and ids for the second GEMM: the softmax runs here, while this warp's
-    // weight rows are on their way (sel_w / sel_id are not read by anyone else any more)
+  if (ids != nullptr) {
+    pdl_wait();
+    inv = stage_row_f16(x + (int64_t)token * H, H, xs, tid, blockDim.x, red);
+    __syncthreads();
+  } else if (bx == 0 && kk == 0 && warp == 0) {
+    // one CTA per token publishes weights and ids for the second GEMM; the softmax runs here, while this warp's
+    // weight rows are on their way
     const __nv_bfloat16* row = logits + (int64_t)token * E;
-    if (E <= 256) router_select<8, __nv_bfloat16>(row, E, top_k, 1, lane, sel_w, sel_id);
-    else router_select<16, __nv_bfloat16>(row, E, top_k, 1, lane, sel_w, sel_id);
+    if (E <= 256) router_weights<8, __nv_bfloat16>(row, E, top_k, 1, lane, sel_id, sel_w);
+    else router_weights<16, __nv_bfloat16>(row, E, top_k, 1, lane, sel_id, sel_w);
+    __syncwarp();
     if (lane < top_k) {
       topk_w_out[token * top_k + lane] = sel_w[lane];
       topk_ids_out[token * top_k + lane] = sel_id[lane];
@@ -482,8 +489,11 @@ struct DenseRegs {
   uint4 qa[4], qb[4];
 };
 
+// trigger_after_wait: raise the launch trigger once this kernel's own dependency wait has passed (everything before
+// this kernel in the stream is then complete, so its successor may read such data before its own wait).
 B200MOE_DEVICE void dense_rows_body(unsigned char* smem_raw, int tile, const __nv_bfloat16* __restrict__ x, int M, int H,
-                                    const DenseSeg& s0, const DenseSeg& s1, const DenseSeg& s2) {
+                                    const DenseSeg& s0, const DenseSeg& s1, const DenseSeg& s2,
+                                    bool trigger_after_wait = false) {
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = blockDim.x >> 5;
   const int g = lane >> 2, t = lane & 3;
   DenseSeg seg = s0;
@@ -529,6 +539,7 @@ B200MOE_DEVICE void dense_rows_body(unsigned char* smem_raw, int tile, const __n
   issue(r0, warp * 128);          // weights depend on nothing: requested before the dependency wait
   issue(r1, warp * 128 + kstep);
   pdl_wait();
+  if (trigger_after_wait) pdl_launch_dependents();
   for (int i = tid * 8; i < 8 * H; i += blockDim.x * 8) {
     const int m = i / H, k = i - m * H;
     uint4 v = make_uint4(0, 0, 0, 0);
@@ -560,8 +571,7 @@ B200MOE_DEVICE void dense_rows_body(unsigned char* smem_raw, int tile, const __n
 __global__ void __launch_bounds__(DENSE_WARPS * 32) dense_rows_kernel(const __nv_bfloat16* __restrict__ x, int M, int H,
                                                                       DenseSeg s0, DenseSeg s1, DenseSeg s2) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  pdl_launch_dependents();
-  dense_rows_body(smem_raw, blockIdx.x, x, M, H, s0, s1, s2);
+  dense_rows_body(smem_raw, blockIdx.x, x, M, H, s0, s1, s2, true);
 }
 
 // ------------------------------------------------------------------------------------------------

@@ -120,4 +120,34 @@ B200MOE_DEVICE void router_select(const LogitT* __restrict__ src, int E, int top
   __syncwarp();
 }
 
+// The weights of experts that are already selected (ids[0..top_k) in selection order, shared or global memory): the
+// same arithmetic as router_select -- softmax over all E logits, the selected probabilities, their sum in selection
+// order, the renormalising division -- without the selection rounds.  One warp; writes w_out[0..top_k), top_k <= 32.
+template <int NPL, typename LogitT>
+B200MOE_DEVICE void router_weights(const LogitT* __restrict__ src, int E, int top_k, int renormalize, int lane,
+                                   const int32_t* ids, float* w_out) {
+  float raw[NPL];
+  float mx = -INFINITY;
+#pragma unroll
+  for (int i = 0; i < NPL; ++i) {
+    const int e = lane + 32 * i;
+    raw[i] = e < E ? (float)src[e] : -INFINITY;
+    mx = fmaxf(mx, raw[i]);
+  }
+  mx = warp_max(mx);
+  float sum = 0.f;
+#pragma unroll
+  for (int i = 0; i < NPL; ++i) {
+    const int e = lane + 32 * i;
+    sum += e < E ? expf(raw[i] - mx) : 0.f;
+  }
+  sum = warp_sum(sum);
+  float p = 0.f;
+  if (lane < top_k) p = expf((float)src[ids[lane]] - mx) / sum;
+  float wsum = 0.f;
+  for (int k = 0; k < top_k; ++k) wsum += __shfl_sync(0xffffffffu, p, k);
+  if (renormalize) p = p / (wsum > 0.f ? wsum : 1.f);
+  if (lane < top_k) w_out[lane] = p;
+}
+
 }  // namespace b200moe
