@@ -48,7 +48,7 @@ def load_peaks() -> dict:
 class ClockSampler:
     """Polls NVML for SM clocks and throttle reasons from a thread while the timed region runs."""
 
-    def __init__(self, index: int, period_s: float = 0.002):
+    def __init__(self, index: int, period_s: float = 0.0005):
         self.index, self.period, self.rows, self.stop = index, period_s, [], threading.Event()
         self.thread, self.max_mhz = None, None
 
