@@ -368,3 +368,34 @@ def test_prefill_other_row_lengths_and_route_counts(hidden, top_k, t):
     rows = ops.prefill_route_rows(d["x"], _banks(d), w.to(DEV), ids.to(DEV))        # route order on request
     summed = ops.combine_routes(rows, ids.to(DEV), shape.num_experts)
     assert torch.equal(summed.view(torch.int16), got.view(torch.int16))
+
+
+def test_prefill_tile_edge_counts():
+    """Routes per expert chosen to hit every tile form and every padding case of the expert-order output: 0, 1, 31,
+    32, 33, 127, 128, 129, 255, 256, 257 and 300 routes (full tiles, 129..255-row tiles, half-form tiles, row groups
+    that end inside a 32-row box)."""
+    counts = [0, 1, 31, 32, 33, 127, 128, 129, 255, 256, 257, 300, 0, 64, 96, 513]
+    shape = synth.Shape(hidden=512, intermediate=256, num_experts=len(counts), top_k=2, shared_intermediate=128)
+    routes = sum(counts)
+    assert routes % 2 == 0
+    t = routes // 2
+    layer = synth.make_layer(71, t, shape)
+    g = torch.Generator().manual_seed(5)
+    flat = torch.cat([torch.full((c,), e, dtype=torch.int32) for e, c in enumerate(counts)])
+    # spread the routes over the tokens so that a token never holds the same expert twice
+    order = torch.argsort(torch.rand(routes, generator=g))
+    ids = torch.full((t, 2), -1, dtype=torch.int32)
+    first, second = [], []
+    for e in flat[order].tolist():
+        (first if len(first) < t else second).append(e)
+    ids[:, 0] = torch.tensor(first, dtype=torch.int32)
+    ids[:, 1] = torch.tensor(second, dtype=torch.int32)
+    clash = ids[:, 0] == ids[:, 1]
+    ids[clash, 1] = -1                      # dropped routes are part of the case
+    w = torch.rand(t, 2, generator=g) * 0.5 + 0.25
+    want = oracle.moe_experts_bf16(layer["x"], layer, w, ids)
+    d = _cuda(layer)
+    got = ops.prefill_experts(d["x"], _banks(d), w.to(DEV), ids.to(DEV), check_status=True)
+    _assert_parity(got, want, "prefill tile edge counts")
+    rows = ops.prefill_route_rows(d["x"], _banks(d), w.to(DEV), ids.to(DEV))
+    assert torch.equal(ops.combine_routes(rows, ids.to(DEV), shape.num_experts).view(torch.int16), got.view(torch.int16))
