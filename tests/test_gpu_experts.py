@@ -399,3 +399,46 @@ def test_prefill_tile_edge_counts():
     _assert_parity(got, want, "prefill tile edge counts")
     rows = ops.prefill_route_rows(d["x"], _banks(d), w.to(DEV), ids.to(DEV))
     assert torch.equal(ops.combine_routes(rows, ids.to(DEV), shape.num_experts).view(torch.int16), got.view(torch.int16))
+
+
+@pytest.mark.parametrize("m,direct", [(1, False), (4, False), (1, True), (8, True)])
+def test_decode_block_chain_where_each_layer_reads_the_previous_output(qwen_layer, m, direct):
+    """The resident block stages x before its dependency wait.  Here every layer's x is produced by the kernel right
+    before it (a residual add + RMSNorm of the previous layer's output), in one CUDA graph, so a read of x that ran
+    ahead of its producer would show: the graph must give the bits of the same chain run with a device
+    synchronisation after every call.  ``direct``: the previous block's output IS the next block's x (the producer
+    is then a kernel that raises its own launch trigger early)."""
+    layer = dict(qwen_layer)
+    d = _cuda(layer)
+    blk = MoEBlock(d["router_w"], d["shared_gate_up"], d["shared_down"], d["shared_gate"], 8)
+    banks = ops.make_banks(_banks(d))
+    g = torch.Generator(device="cuda").manual_seed(3)
+    norm_w = (torch.rand(d["x"].shape[1], generator=g, device="cuda") + 0.5).bfloat16()
+    depth = 6
+
+    def chain(x0, sync):
+        h, res = x0.clone(), torch.zeros_like(x0)
+        outs = []
+        for _ in range(depth):
+            if not direct:
+                ops.fused_add_rmsnorm(h, res, norm_w, 1e-6)  # h = norm(h + res), res = h + res: h is this layer's x
+            out = torch.empty_like(h)
+            blk.decode_fused(h, banks, out)
+            if sync:
+                torch.cuda.synchronize()
+            outs.append(out)
+            h = out if direct else out.clone()
+        return torch.stack(outs)
+
+    x0 = d["x"][:m].contiguous()
+    want = chain(x0, True)
+    x_buf = x0.clone()
+    chain(x_buf, False)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        got = chain(x_buf, False)
+    for rep in range(5):
+        graph.replay()
+        torch.cuda.synchronize()
+        assert torch.equal(got.view(torch.int16), want.view(torch.int16)), rep
